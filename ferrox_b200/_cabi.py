@@ -66,6 +66,13 @@ def _sigs(real):
         "softmax_ce": (I, [H, _P, _P, _P, _P, I64, I64, real, S]),
         "sgd_step": (I, [H, _P, _P, _P, I64, real, real, real, I, real, S]),
         "adam_step": (I, [H, _P, _P, _P, _P, I64, real, real, real, real, real, I64, real, S]),
+        "materialize": (I, [H, _P, _P, POINTER(c_int64), POINTER(c_int64), I, S]),
+        "transpose": (I, [H, _P, _P, POINTER(c_int64), I, POINTER(c_int), S]),
+        "broadcast_to": (I, [H, _P, POINTER(c_int64), I, _P, POINTER(c_int64), I, S]),
+        "batch_norm_fwd": (I, [H, _P, _P, _P, _P, _P, _P, _P, _P, I64, I64, I64, c_double, c_double, I, I, _P, SZ, S]),
+        "batch_norm_bwd": (I, [H, _P, _P, _P, _P, _P, _P, _P, _P, _P, I64, I64, I64, c_double, I, _P, SZ, S]),
+        "global_avg_pool_fwd": (I, [H, _P, _P, I64, I64, I64, I64, S]),
+        "global_avg_pool_bwd": (I, [H, _P, _P, I64, I64, I64, I64, S]),
     }
 
 
@@ -78,6 +85,7 @@ _COMMON = {
     "fxb_set_operand_path": (c_int, [c_void_p, c_int]),
     "fxb_set_sigmoid_grad_mode": (c_int, [c_void_p, c_int]),
     "fxb_check_device_status": (c_int, [c_void_p, c_void_p]),
+    "fxb_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),
     "fxb_version": (c_int, []),
     "fxb_launch_count": (ctypes.c_uint64, [c_void_p]),
     "fxb_gemm_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
@@ -85,7 +93,9 @@ _COMMON = {
     "fxb_conv2d_wgrad_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_conv2d_fprop_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_conv2d_fprop_prepass_f32": (c_int, [c_void_p, c_void_p, c_void_p, _DP, c_void_p, c_size_t, c_void_p]),
+    "fxb_conv2d_fprop_main_f32": (c_int, [c_void_p, c_void_p, c_void_p, _DP, c_int, c_void_p, c_size_t, c_void_p]),
     "fxb_conv2d_dgrad_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
+    "fxb_batch_norm_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
     "fxb_sum_axes_workspace_bytes": (c_size_t, [c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_size_t]),
     "fxb_sum_axes_static_scratch_f32": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_void_p,
                                                 c_void_p]),

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libferrox_b200.so")
-SOURCES = ["fxb_api.cu", "fxb_contract.cu", "fxb_stream.cu", "fxb_net.cu"]
+SOURCES = ["fxb_api.cu", "fxb_contract.cu", "fxb_stream.cu", "fxb_net.cu", "fxb_layout.cu", "fxb_norm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -7,7 +7,38 @@ namespace fxb {
 thread_local std::string g_tls_error;
 }
 
-extern "C" int fxb_version(void) { return 100; }
+extern "C" int fxb_version(void) { return 110; }
+
+namespace fxb {
+// Self-test of the bounded-wait convention every kernel of the library follows: one warp waits on an
+// mbarrier that nobody ever arrives on (no copy and no MMA is in flight, no TMEM is held).  When the
+// cycle limit runs out the wait records its tag in the status block and the kernel returns normally.
+constexpr int SELFTEST_WAIT_TAG = 99;
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(DeviceStatus* status, long long limit_cycles, int* gave_up) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        mbar_init_fence();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        const bool done = mbar_wait_bounded(smem_u32(&bar), 0u, &abort_flag, status, SELFTEST_WAIT_TAG, limit_cycles);
+        *gave_up = done ? 0 : 1;
+    }
+}
+}  // namespace fxb
+
+extern "C" int fxb_selftest_bounded_wait(fxb_handle_t h, int64_t limit_cycles, fxb_stream_t stream) {
+    if (h == nullptr) return fail(nullptr, FXB_ERR_INVALID_ARGUMENT, "null ferrox_b200 handle");
+    Context* c = reinterpret_cast<Context*>(h);
+    FXB_CHECK_ARG(c, limit_cycles > 0 && limit_cycles <= 100000000LL, "fxb_selftest_bounded_wait: limit must be in (0, 1e8] cycles");
+    // the flag lives in the handle's scratch block, past the loss kernel's counter and partial sums
+    int* gave_up = reinterpret_cast<int*>(static_cast<char*>(c->d_scratch) + 8192 - 64);
+    bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(c->d_status, (long long)limit_cycles, gave_up);
+    return launch_status(c, "bounded_wait_selftest_kernel");
+}
 
 extern "C" uint64_t fxb_launch_count(fxb_handle_t h) {
     return h ? reinterpret_cast<Context*>(h)->launches : 0;
@@ -52,10 +83,18 @@ extern "C" int fxb_create(int device, fxb_handle_t* out) {
     e = cudaMalloc(reinterpret_cast<void**>(&c->d_status), sizeof(DeviceStatus) + 8192);
     if (e == cudaSuccess) e = cudaMemset(c->d_status, 0, sizeof(DeviceStatus) + 8192);
     c->d_scratch = reinterpret_cast<char*>(c->d_status) + sizeof(DeviceStatus);
+    // the static scratch array's device address, looked up while this device is current
+    const int rs = e == cudaSuccess ? resolve_static_scratch(c) : FXB_OK;
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         delete c;
         return fail(nullptr, FXB_ERR_CUDA, std::string("fxb_create: status block: ") + cudaGetErrorString(e));
+    }
+    if (rs != FXB_OK) {
+        const std::string msg = c->last_error;
+        cudaFree(c->d_status);
+        delete c;
+        return fail(nullptr, rs, "fxb_create: " + msg);
     }
     *out = reinterpret_cast<fxb_handle_t>(c);
     return FXB_OK;

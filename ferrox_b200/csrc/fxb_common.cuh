@@ -29,16 +29,19 @@ struct Context {
     int math_mode = FXB_MATH_3XTF32;
     int sigmoid_grad_math = 0;  // 0 = the reference's literal s*(s-1); 1 = s*(1-s)
     int operand_path = 0;       // FXB_PATH_*: which operand paths the f32 convolutions may take
-    int stop_after_prepass = 0; // set by fxb_conv2d_fprop_prepass_f32 only
     DeviceStatus* d_status = nullptr;
     // 8 KB of handle-owned device scratch right after the status block (per-CTA partial sums of the
     // loss kernel + its arrival counter); used by one stream at a time, like the handle itself.
     void* d_scratch = nullptr;
+    // device address of the library's static 512 KiB scratch array (fxb_sum_axes_static_scratch_f32),
+    // resolved once by fxb_create with this device current
+    void* static_scratch = nullptr;
     unsigned long long launches = 0;  // kernels launched through this handle
     std::string last_error;
 };
 
 extern thread_local std::string g_tls_error;  // defined in fxb_api.cu
+int resolve_static_scratch(Context* c);        // defined in fxb_stream.cu, beside the array
 
 inline int fail(Context* ctx, int code, const std::string& msg) {
     if (ctx) ctx->last_error = msg;

@@ -411,6 +411,8 @@ static int launch_dmma_bn(Context* c, const LA& la, const LB& lb, OutputWriter<d
         if (rsa) { rsa = rs; rs += (size_t)splits * p.M; }
         if (rsb) rsb = rs;
     }
+    if (tn > 65535 || splits > 65535)
+        return fail(c, FXB_ERR_UNSUPPORTED, "f64 contraction: more than 65535 column tiles (N > 4 million) is not supported");
     dim3 grid(tm, tn, splits);
     kern<<<grid, DMMA_THREADS, Cfg::SMEM_BYTES, st>>>(la, lb, ow, shp, rsa, rsb);
     int rc = launch_status(c, "dmma_contract_kernel");
@@ -668,8 +670,10 @@ static void set_vec_store(TmaConvParams& prm) {
 
 // Forward convolution on the TMA engine.  *used = false (and FXB_OK) when the shapes cannot be
 // described by tensor maps; the caller then takes the cp.async path.
+// phase: which part of the call runs (FPROP_ALL, or one half for timing the two separately).
+enum : int { FPROP_ALL = 0, FPROP_PREPASS_ONLY = 1, FPROP_MAIN_ONLY = 2 };
 static int conv_fprop_tma(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
-                          int act, void* ws, cudaStream_t st, bool* used) {
+                          int act, void* ws, cudaStream_t st, bool* used, int phase = FPROP_ALL) {
     *used = false;
     if (!tma_stride_ok(g) || tensor_map_encoder() == nullptr) return FXB_OK;
     const TmaFpropLayout l = tma_fprop_layout(g);
@@ -681,7 +685,7 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     if (!encode_slab_maps(prm, w.a_hi, w.a_lo, l.Wc, l.Hc, l.planes, g.N, pp, l.Q)) return FXB_OK;
     if (!encode_filter_maps(prm, w.b_hi, w.b_lo, l.rows_pad, g.RS * l.Q, bn)) return FXB_OK;
     *used = true;
-    {
+    if (phase != FPROP_MAIN_ONLY) {
         const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
         const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
         split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
@@ -696,7 +700,7 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
         rc = launch_status(c, "split_filter_chunk_major_kernel");
         if (rc) return rc;
     }
-    if (c->stop_after_prepass) return FXB_OK;
+    if (phase == FPROP_PREPASS_ONLY) return FXB_OK;
     set_patch(prm, pp, g.N, g.OH, g.OW);
     prm.tn = (g.K + bn - 1) / bn;
     prm.ncols = g.K;
@@ -735,18 +739,19 @@ static int conv_fprop_async(Context* c, const float* X, const float* W, const fl
 
 template <typename T>
 static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T* Y, const fxb_conv2d_desc* d, int act,
-                           void* ws, size_t ws_bytes, cudaStream_t st) {
+                           void* ws, size_t ws_bytes, cudaStream_t st, int phase = FPROP_ALL) {
     ConvGeom g;
     int rc = make_geom(c, d, g);
     if (rc) return rc;
     FXB_CHECK_ARG(c, X && W && Y, "Conv2D got a null buffer");
     FXB_CHECK_ARG(c, act >= FXB_ACT_NONE && act <= FXB_ACT_TANH, "Unknown activation code");
-    if (c->stop_after_prepass) {
-        // pre-pass only: nothing but the tensor-map path may run (any other path would write an output)
+    if (phase != FPROP_ALL) {
+        // one half only: nothing but the tensor-map path has two halves
         if constexpr (sizeof(T) == 4) {
             bool used = false;
-            if ((reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes >= fprop_split_bytes(g) && g.CRS > SMALLC_K)
-                rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used);
+            if (c->operand_path == FXB_PATH_AUTO && ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 &&
+                ws_bytes >= fprop_split_bytes(g) && g.CRS > SMALLC_K)
+                rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, phase);
             if (rc) return rc;
             if (used) return FXB_OK;
         }
@@ -1203,7 +1208,8 @@ static int linear_bwd_impl(Context* c, const T* X, const T* W, const T* Y, const
     FXB_CHECK_ARG(c, X && W && dY && dW, "Linear backward got a null buffer");
     FXB_CHECK_ARG(c, act == FXB_ACT_NONE || Y != nullptr, "Fused activation backward needs the layer output");
     const T* aux = act == FXB_ACT_NONE ? nullptr : Y;
-    if (out <= SKINNY_MAXO && fits_i32(B) && fits_i32(in) && B <= 65535 * (int64_t)SKINNY_ROWS) {
+    // grid limits of the three kernels: chunks of 128 rows and blocks of 256 columns in grid.y (<= 65535)
+    if (out <= SKINNY_MAXO && fits_i32(B) && fits_i32(in) && B <= 65535 * (int64_t)SKINNY_ROWS && in <= 65535 * (int64_t)256) {
         const int chunks = (int)((B + SKINNY_ROWS - 1) / SKINNY_ROWS);
         const size_t need = skinny_bwd_bytes<T>(B, in, out);
         if (chunks == 1 || (ws != nullptr && ws_bytes >= need)) {
@@ -1223,7 +1229,7 @@ static int linear_bwd_impl(Context* c, const T* X, const T* W, const T* Y, const
                 if (rc) return rc;
             }
             if (dX) {
-                dim3 gx((unsigned)((in + 255) / 256), (unsigned)B);
+                dim3 gx((unsigned)B, (unsigned)((in + 255) / 256));
                 skinny_linear_dx_kernel<T><<<gx, 256, 0, st>>>(dY, aux, W, dX, (int)in, (int)out, act, c->sigmoid_grad_math);
                 rc = launch_status(c, "skinny_linear_dx_kernel");
             }
@@ -1324,11 +1330,19 @@ extern "C" int fxb_conv2d_fprop_prepass_f32(fxb_handle_t h, const float* X, cons
     Context* c = CTX(h);
     if (c->operand_path != FXB_PATH_AUTO || ws == nullptr)
         return fail(c, FXB_ERR_INVALID_ARGUMENT, "the operand pre-pass needs FXB_PATH_AUTO and a workspace");
-    c->stop_after_prepass = 1;
-    // the output pointer is not touched when the pre-pass stops before the contraction
-    const int rc = conv_fprop_impl<float>(c, X, W, nullptr, reinterpret_cast<float*>(ws), d, FXB_ACT_NONE, ws, ws_bytes, ST(s));
-    c->stop_after_prepass = 0;
-    return rc;
+    // the output pointer is not touched when the call stops before the contraction
+    return conv_fprop_impl<float>(c, X, W, nullptr, reinterpret_cast<float*>(ws), d, FXB_ACT_NONE, ws, ws_bytes, ST(s),
+                                  FPROP_PREPASS_ONLY);
+}
+extern "C" int fxb_conv2d_fprop_main_f32(fxb_handle_t h, const float* bias, float* Y, const fxb_conv2d_desc* d, int act,
+                                         void* ws, size_t ws_bytes, fxb_stream_t s) {
+    NEED_HANDLE(h);
+    Context* c = CTX(h);
+    if (c->operand_path != FXB_PATH_AUTO || ws == nullptr)
+        return fail(c, FXB_ERR_INVALID_ARGUMENT, "the contraction-only call needs FXB_PATH_AUTO and the pre-pass workspace");
+    // X and W are not read: the operands come from the workspace the pre-pass filled
+    return conv_fprop_impl<float>(c, reinterpret_cast<const float*>(ws), reinterpret_cast<const float*>(ws), bias, Y, d, act, ws,
+                                  ws_bytes, ST(s), FPROP_MAIN_ONLY);
 }
 extern "C" size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
     if (!h || !d || elem != 4) return 0;

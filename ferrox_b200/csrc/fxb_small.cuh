@@ -50,20 +50,21 @@ __global__ void __launch_bounds__(256) skinny_linear_fwd_kernel(const T* __restr
     }
 }
 
-// dX[b][i] = sum_o dZ[b][o] * W[o][i], dZ = dY * act'(Y); grid (ceil(in/256), B).
+// dX[b][i] = sum_o dZ[b][o] * W[o][i], dZ = dY * act'(Y); grid (B, ceil(in/256)): the batch index is
+// the x dimension of the grid, which has no 65535 limit.
 template <typename T>
 __global__ void __launch_bounds__(256) skinny_linear_dx_kernel(const T* __restrict__ dY, const T* __restrict__ Yact,
                                                                const T* __restrict__ W, T* __restrict__ dX, int in, int out,
                                                                int act, int sig_math) {
     __shared__ T dz[SKINNY_MAXO];
-    const int b = blockIdx.y;
+    const int b = blockIdx.x;
     if (threadIdx.x < out) {
         T v = __ldg(dY + (int64_t)b * out + threadIdx.x);
         if (Yact) v *= act_grad_factor<T>(__ldg(Yact + (int64_t)b * out + threadIdx.x), act, sig_math);
         dz[threadIdx.x] = v;
     }
     __syncthreads();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= in) return;
     T acc = T(0);
 #pragma unroll

@@ -211,13 +211,14 @@ __global__ void __launch_bounds__(256) reduce_inner_kernel(const T* __restrict__
 // independent row loads are in flight per thread.
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_outer_kernel(const T* __restrict__ x, T* __restrict__ part, ReduceGeom g,
-                                                           FastDiv dk0, FastDiv dr1, int vec_ok) {
+                                                           FastDiv dk0, FastDiv dr1, FastDiv dct, int vec_ok) {
     constexpr int V = VecOf<T>::N;
     __shared__ T red[8][32 * V + 1];
     const int cg = threadIdx.x & 31, rl = threadIdx.x >> 5;
-    const int64_t col0 = ((int64_t)blockIdx.x * 32 + cg) * V;
-    const uint32_t o = blockIdx.y;  // kb*K0 + k0
-    const int p = blockIdx.z;
+    uint32_t o, ct;  // kept outer index kb*K0 + k0 and column tile, both folded into grid.x
+    dct.divmod(blockIdx.x, o, ct);
+    const int64_t col0 = ((int64_t)ct * 32 + cg) * V;
+    const int p = blockIdx.y;
     uint32_t kb, k0;
     dk0.divmod(o, kb, k0);
     const uint32_t rows = (uint32_t)(g.R0 * g.R1);
@@ -371,9 +372,10 @@ static int sum_axes_impl(Context* c, const T* x, const int64_t* shape, int ndim,
     } else {
         const int vec_ok = al && (g.K1 % V == 0);
         const int64_t ctiles = (g.K1 + 32 * V - 1) / (32 * V);
-        FXB_CHECK_ARG(c, g.KB * g.K0 < 65536, "sum_axes: too many kept outer rows for the column kernel");
-        dim3 grid((unsigned)ctiles, (unsigned)(g.KB * g.K0), (unsigned)g.parts);
-        reduce_outer_kernel<T><<<grid, 256, 0, st>>>(x, part, g, FastDiv((uint32_t)g.K0), FastDiv((uint32_t)g.R1), vec_ok);
+        FXB_CHECK_ARG(c, ctiles * g.KB * g.K0 < ((int64_t)1 << 31), "sum_axes: too many outputs");
+        dim3 grid((unsigned)(ctiles * g.KB * g.K0), (unsigned)g.parts);
+        reduce_outer_kernel<T><<<grid, 256, 0, st>>>(x, part, g, FastDiv((uint32_t)g.K0), FastDiv((uint32_t)g.R1),
+                                                     FastDiv((uint32_t)ctiles), vec_ok);
     }
     rc = launch_status(c, "reduce_sum stage 1");
     if (rc) return rc;
@@ -385,12 +387,80 @@ static int sum_axes_impl(Context* c, const T* x, const int64_t* shape, int ndim,
     return rc;
 }
 
-static size_t sum_axes_ws(Context* c, const int64_t* shape, int ndim, const int* axes, int naxes, size_t elem) {
+static size_t sum_axes_ws_one(Context* c, const int64_t* shape, int ndim, const int* axes, int naxes, size_t elem) {
     ReduceGeom g;
     bool any = false;
     if (collapse_axes(c, shape, ndim, axes, naxes, g, any) != FXB_OK || !any || g.outputs == 0) return 0;
     g.parts = pick_parts(c, g);
     return g.parts > 1 ? (size_t)g.parts * g.outputs * elem : 0;
+}
+
+// One launch pair handles at most two separate runs of reduced axes.  With more (a 5-D or larger
+// tensor reduced over alternating axes) the two innermost runs are reduced first into an
+// intermediate tensor at the front of the workspace, and the rest in a second round.
+// Returns false when the axes form at most two runs (or are invalid: the single-round code reports that).
+struct AxisSplit {
+    int first_axes[8], nfirst, rest_axes[8], nrest, mid_ndim;
+    int64_t mid_shape[8], mid_elems;
+};
+static bool split_reduced_runs(const int64_t* shape, int ndim, const int* axes, int naxes, AxisSplit& sp) {
+    if (ndim < 5 || ndim > 8) return false;
+    bool red[8] = {};
+    for (int i = 0; i < naxes; ++i) {
+        if (axes[i] < 0 || axes[i] >= ndim) return false;
+        red[axes[i]] = true;
+    }
+    int run_of[8], runs = 0;
+    bool in_run = false;
+    for (int i = 0; i < ndim; ++i) {
+        run_of[i] = -1;
+        if (shape[i] == 1) continue;  // size-1 dimensions neither join nor separate runs
+        if (red[i]) {
+            if (!in_run) { ++runs; in_run = true; }
+            run_of[i] = runs - 1;
+        } else {
+            in_run = false;
+        }
+    }
+    if (runs <= 2) return false;
+    sp.nfirst = sp.nrest = sp.mid_ndim = 0;
+    sp.mid_elems = 1;
+    for (int i = 0; i < ndim; ++i) {
+        const bool first = red[i] && (shape[i] == 1 || run_of[i] >= runs - 2);
+        if (first) { sp.first_axes[sp.nfirst++] = i; continue; }
+        if (red[i]) sp.rest_axes[sp.nrest++] = sp.mid_ndim;
+        sp.mid_shape[sp.mid_ndim++] = shape[i];
+        sp.mid_elems *= shape[i];
+    }
+    return true;
+}
+static size_t align_up256s(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static size_t sum_axes_ws(Context* c, const int64_t* shape, int ndim, const int* axes, int naxes, size_t elem) {
+    AxisSplit sp;
+    if (!split_reduced_runs(shape, ndim, axes, naxes, sp)) return sum_axes_ws_one(c, shape, ndim, axes, naxes, elem);
+    const size_t a = sum_axes_ws_one(c, shape, ndim, sp.first_axes, sp.nfirst, elem);
+    const size_t b = sum_axes_ws(c, sp.mid_shape, sp.mid_ndim, sp.rest_axes, sp.nrest, elem);
+    return align_up256s((size_t)sp.mid_elems * elem) + std::max(a, b);
+}
+
+template <typename T>
+static int sum_axes_any(Context* c, const T* x, const int64_t* shape, int ndim, const int* axes, int naxes, T* out,
+                        void* ws, size_t ws_bytes, cudaStream_t st) {
+    AxisSplit sp;
+    if (shape == nullptr || axes == nullptr || !split_reduced_runs(shape, ndim, axes, naxes, sp))
+        return sum_axes_impl<T>(c, x, shape, ndim, axes, naxes, out, ws, ws_bytes, st);
+    if (sp.mid_elems == 0) return FXB_OK;
+    const size_t mid_bytes = align_up256s((size_t)sp.mid_elems * sizeof(T));
+    if (ws == nullptr || ws_bytes < mid_bytes)
+        return fail(c, FXB_ERR_WORKSPACE,
+                    "sum_axes: more than two separate runs of reduced axes need a workspace of fxb_sum_axes_workspace_bytes");
+    T* mid = static_cast<T*>(ws);
+    char* rest_ws = static_cast<char*>(ws) + mid_bytes;
+    const size_t rest_bytes = ws_bytes - mid_bytes;
+    const int rc = sum_axes_impl<T>(c, x, shape, ndim, sp.first_axes, sp.nfirst, mid, rest_ws, rest_bytes, st);
+    if (rc) return rc;
+    return sum_axes_any<T>(c, mid, sp.mid_shape, sp.mid_ndim, sp.rest_axes, sp.nrest, out, rest_ws, rest_bytes, st);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -534,23 +604,16 @@ static int flat_grid(const Context* c, int64_t n) {
 constexpr size_t STATIC_SCRATCH_BYTES = (size_t)512 << 10;
 static __device__ __align__(256) unsigned char g_sum_scratch[STATIC_SCRATCH_BYTES];
 
-// `g_sum_scratch` in host code is only a host-side handle for the symbol, not a device address;
-// the device address is looked up once per device (with that device current) and cached.
-static int static_scratch_address(Context* c, void** out) {
-    static void* cached[64] = {};
-    const int slot = c->device & 63;
-    if (cached[slot] == nullptr) {
-        int prev = 0;
-        FXB_CUDA_OK(c, cudaGetDevice(&prev));
-        if (prev != c->device) FXB_CUDA_OK(c, cudaSetDevice(c->device));
-        void* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(&p, g_sum_scratch);
-        if (prev != c->device) cudaSetDevice(prev);
-        if (e != cudaSuccess || p == nullptr)
-            return fail(c, FXB_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
-        cached[slot] = p;
-    }
-    *out = cached[slot];
+// `g_sum_scratch` in host code is only a host-side handle for the symbol, not a device address.
+// fxb_create calls this once per handle, with the handle's device current, and keeps the device
+// address in the context, so that the entry point below never touches the module loader or the
+// current device (its callers may be inside an out-of-memory handler).
+int resolve_static_scratch(Context* c) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_sum_scratch);
+    if (e != cudaSuccess || p == nullptr)
+        return fail(c, FXB_ERR_CUDA, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e));
+    c->static_scratch = p;
     return FXB_OK;
 }
 
@@ -561,8 +624,8 @@ static int static_scratch_address(Context* c, void** out) {
 //    library's static 512 KiB device array.
 //  - A reduction whose partial sums need more than that is refused with FXB_ERR_WORKSPACE
 //    (nothing is launched); use fxb_sum_axes_f32 with a pool workspace for those.
-//  - The first call on a device looks up the array's device address (cudaGetSymbolAddress);
-//    make that first call outside any stream capture.
+//  - The array's device address was looked up by fxb_create (cudaGetSymbolAddress with the handle's
+//    device current), so this call touches neither the module loader nor the current device.
 //  - Every call on a device shares the one array and leaves its partial sums behind.  Nothing
 //    in it has to be zero beforehand (stage one overwrites every slot stage two reads), but two
 //    calls that overlap on the GPU (different streams, no ordering) would race on it.
@@ -576,11 +639,10 @@ extern "C" int fxb_sum_axes_static_scratch_f32(fxb_handle_t h, const float* x, c
                          "fxb_sum_axes_static_scratch_f32: this reduction needs " + std::to_string(need) +
                              " bytes of partial sums, the static scratch holds " +
                              std::to_string(fxb::STATIC_SCRATCH_BYTES) + "; use fxb_sum_axes_f32 with a workspace");
-    void* scratch = nullptr;
-    const int rc = fxb::static_scratch_address(c, &scratch);
-    if (rc != FXB_OK) return rc;
-    return fxb::sum_axes_impl<float>(c, x, shape, ndim, axes, naxes, out, scratch, fxb::STATIC_SCRATCH_BYTES,
-                                     static_cast<cudaStream_t>(stream));
+    if (c->static_scratch == nullptr)
+        return fxb::fail(c, FXB_ERR_CUDA, "fxb_sum_axes_static_scratch_f32: the static scratch address was not resolved by fxb_create");
+    return fxb::sum_axes_any<float>(c, x, shape, ndim, axes, naxes, out, c->static_scratch, fxb::STATIC_SCRATCH_BYTES,
+                                    static_cast<cudaStream_t>(stream));
 }
 
 
@@ -637,7 +699,7 @@ using namespace fxb;
     extern "C" int fxb_sum_axes_##SUF(fxb_handle_t h, const T* x, const int64_t* shape, int ndim, const int* axes,      \
                                       int naxes, T* out, void* ws, size_t wsb, fxb_stream_t s) {                        \
         NEED_HANDLE(h);                                                                                                 \
-        return sum_axes_impl<T>(CTX(h), x, shape, ndim, axes, naxes, out, ws, wsb, ST(s));                              \
+        return sum_axes_any<T>(CTX(h), x, shape, ndim, axes, naxes, out, ws, wsb, ST(s));                               \
     }                                                                                                                   \
     extern "C" int fxb_sum_all_##SUF(fxb_handle_t h, const T* x, int64_t n, T* out, void* ws, size_t wsb,               \
                                      fxb_stream_t s) {                                                                  \

@@ -121,6 +121,10 @@ class CudaOps:
     def check_device_status(self):
         self._check(self.lib.fxb_check_device_status(self.h, self._stream()))
 
+    def selftest_bounded_wait(self, limit_cycles=1_000_000):
+        """Launches the library's bounded-wait self-test kernel (a wait that must run out)."""
+        self._check(self.lib.fxb_selftest_bounded_wait(self.h, int(limit_cycles), self._stream()))
+
     @staticmethod
     def _desc(x_shape, w_shape, stride, padding):
         N, C, H, W = x_shape
@@ -190,6 +194,18 @@ class CudaOps:
         nb = self.lib.fxb_conv2d_fprop_workspace_bytes(self.h, ctypes.byref(d), x.element_size())
         ws, wsb = self.workspace(nb, x.device)
         self._check(self.lib.fxb_conv2d_fprop_prepass_f32(self.h, _ptr(x), _ptr(w), ctypes.byref(d), _ptr(ws), wsb, self._stream()))
+
+    def conv2d_forward_main(self, x_shape, w_shape, stride, padding, bias=None, act=None, like=None):
+        """Only the contraction kernel of the f32 conv2d_forward, on the operands the last
+        conv2d_forward_prepass call for the same shapes left in the workspace."""
+        d = self._desc(x_shape, w_shape, stride, padding)
+        like = bias if like is None else like
+        out = self._get_tensor(self.conv_out_shape(x_shape, w_shape, stride, padding), like)
+        nb = self.lib.fxb_conv2d_fprop_workspace_bytes(self.h, ctypes.byref(d), 4)
+        ws, wsb = self.workspace(nb, like.device)
+        self._check(self.lib.fxb_conv2d_fprop_main_f32(self.h, _ptr(bias), _ptr(out), ctypes.byref(d), act_code(act), _ptr(ws), wsb,
+                                                       self._stream()))
+        return out
 
     def deconv2d(self, dy, w, input_shape, stride, padding, y=None, act=None):
         """CudaOps::deconv2d (ops.rs:1458-1539): gradient w.r.t. the conv input."""
@@ -322,6 +338,102 @@ class CudaOps:
         ws, wsb = self.workspace(nb, x.device)
         self._check(self._fn("sum_all", x)(self.h, _ptr(x), x.numel(), _ptr(out), _ptr(ws), wsb, self._stream()))
         return out
+
+    # ------------------------------------------------------------------ layout ops
+    def materialize(self, t):
+        """CudaOps::materialize (ops.rs:175-214): a strided / broadcast view (any torch view whose strides
+        are non-negative) copied into new contiguous memory by the library's layout kernels."""
+        if not t.is_cuda:
+            raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT, "tensor is not on a CUDA device")
+        out = self._get_tensor(t.shape, t)
+        nd = max(1, t.dim())
+        shape = (c_int64 * nd)(*t.shape)
+        strides = (c_int64 * nd)(*t.stride())
+        self._check(self._fn("materialize", t)(self.h, _ptr(t), _ptr(out), shape, strides, t.dim(), self._stream()))
+        return out
+
+    def transpose(self, x, axes=None):
+        """Transpose::compute (src/ops/matrix.rs:69-110) followed by the materialisation every consumer
+        triggers: the permuted tensor in contiguous memory.  axes=None reverses all axes."""
+        x = self._in(x)
+        nd = x.dim()
+        perm = list(range(nd - 1, -1, -1)) if axes is None else list(axes)
+        if sorted(perm) != list(range(nd)):
+            raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT, f"transpose: axes must be a permutation of 0..{nd - 1}")
+        out = self._get_tensor([x.shape[a] for a in perm], x)
+        shape = (c_int64 * max(1, nd))(*x.shape)
+        ax = None if axes is None else (c_int * max(1, nd))(*perm)
+        self._check(self._fn("transpose", x)(self.h, _ptr(x), _ptr(out), shape, nd, ax, self._stream()))
+        return out
+
+    def broadcast_to(self, x, shape):
+        """broadcast_to + materialize (src/backend/storage/cuda.rs:795-803)."""
+        x = self._in(x)
+        shape = list(shape)
+        if x.dim() > len(shape):
+            raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT, "broadcast_to: the target must have at least as many dimensions")
+        out = self._get_tensor(shape, x)
+        ins = (c_int64 * max(1, x.dim()))(*x.shape)
+        outs = (c_int64 * max(1, len(shape)))(*shape)
+        self._check(self._fn("broadcast_to", x)(self.h, _ptr(x), ins, x.dim(), _ptr(out), outs, len(shape), self._stream()))
+        return out
+
+    # ------------------------------------------------------------------ normalisation and pooling
+    @staticmethod
+    def _ncp(x):
+        if x.dim() < 2:
+            raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT, "BatchNorm requires at least 2D input [batch_size, features]")
+        n, ch = x.shape[0], x.shape[1]
+        return n, ch, x.numel() // max(1, n * ch)
+
+    def batch_norm_forward(self, x, gamma, beta, eps=1e-5, momentum=0.1, running_mean=None, running_var=None, training=True,
+                           act=None):
+        """BatchNorm::forward (src/nn/layers/norm.rs:214-331).  Training returns (y, batch_mean, batch_var)
+        and updates the running statistics in place when given; inference returns y."""
+        x = self._in(x)
+        n, ch, p = self._ncp(x)
+        y = self._get_tensor(x.shape, x)
+        if training:
+            mean, var = self._get_tensor((ch,), x), self._get_tensor((ch,), x)
+            nb = self.lib.fxb_batch_norm_workspace_bytes(self.h, n, ch, p, x.element_size())
+            ws, wsb = self.workspace(nb, x.device)
+        else:
+            mean = var = ws = None
+            wsb = 0
+        self._check(self._fn("batch_norm_fwd", x)(self.h, _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(mean), _ptr(var),
+                                                  _ptr(running_mean), _ptr(running_var), n, ch, p, eps, momentum, int(training),
+                                                  act_code(act), _ptr(ws), wsb, self._stream()))
+        return (y, mean, var) if training else y
+
+    def batch_norm_backward(self, x, dy, gamma, batch_mean, batch_var, eps=1e-5, y=None, act=None, need_dx=True):
+        """(dX, dgamma, dbeta) of the fused batch-norm (+ activation) layer."""
+        x, dy = self._in(x), self._in(dy)
+        n, ch, p = self._ncp(x)
+        dx = self._get_tensor(x.shape, x) if need_dx else None
+        dg, db = self._get_tensor((ch,), x), self._get_tensor((ch,), x)
+        nb = self.lib.fxb_batch_norm_workspace_bytes(self.h, n, ch, p, x.element_size())
+        ws, wsb = self.workspace(nb, x.device)
+        self._check(self._fn("batch_norm_bwd", x)(self.h, _ptr(x), _ptr(dy), _ptr(None if y is None else self._in(y)), _ptr(gamma),
+                                                  _ptr(batch_mean), _ptr(batch_var), _ptr(dx), _ptr(dg), _ptr(db), n, ch, p, eps,
+                                                  act_code(act), _ptr(ws), wsb, self._stream()))
+        return dx, dg, db
+
+    def global_avg_pool_forward(self, x, flatten=True):
+        """GlobalAvgPool2d::forward (src/nn/layers/pooling.rs:604-619): [N,C,H,W] -> [N,C] (or [N,C,1,1])."""
+        x = self._in(x)
+        if x.dim() != 4:
+            raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT, "GlobalAvgPool2d requires 4D input [batch, channels, height, width]")
+        n, ch, hh, ww = x.shape
+        y = self._get_tensor((n, ch) if flatten else (n, ch, 1, 1), x)
+        self._check(self._fn("global_avg_pool_fwd", x)(self.h, _ptr(x), _ptr(y), n, ch, hh, ww, self._stream()))
+        return y
+
+    def global_avg_pool_backward(self, dy, input_shape):
+        dy = self._in(dy)
+        n, ch, hh, ww = input_shape
+        dx = self._get_tensor(input_shape, dy)
+        self._check(self._fn("global_avg_pool_bwd", dy)(self.h, _ptr(dy), _ptr(dx), n, ch, hh, ww, self._stream()))
+        return dx
 
     # ------------------------------------------------------------------ fused layer ops
     def linear_forward(self, x, w, bias=None, act=None):

@@ -224,7 +224,11 @@ class Trainer:
         return net.loss_slot
 
     def loss_value(self):
-        """Global mean loss of the last step (one device-to-host read)."""
+        """Global mean loss of the last step (one device-to-host read).  This is the step's only
+        synchronisation point, so the device status word is read here as well: a bounded wait that
+        ran out in any kernel of the step raises FerroxB200Error instead of letting the optimizer
+        go on with partly written gradients."""
+        self.ops.check_device_status()
         v = float(self.net.loss_slot.item())
         return v / self.world if self.world > 1 else v
 

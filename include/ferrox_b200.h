@@ -8,7 +8,8 @@
  * Conventions (all taken from how the reference drives its kernels):
  *  - Buffers are raw device pointers to contiguous row-major data (NCHW for images, KCRS for
  *    filters); the library never allocates, frees or resizes tensor memory — outputs and
- *    scratch come from the caller's pool (src/backend/cuda/ops.rs:121-133).
+ *    scratch come from the caller's pool (src/backend/cuda/ops.rs:121-133).  The only device
+ *    memory it owns is an 8 KB status / counter block per handle, allocated by fxb_create.
  *  - Outputs are written in full: a recycled pool buffer may hold stale data and may be
  *    longer than requested (src/backend/cuda/context.rs:72).
  *  - Every call is asynchronous on the caller's stream (the reference's "compute" stream,
@@ -80,6 +81,11 @@ int fxb_set_sigmoid_grad_mode(fxb_handle_t h, int math_mode);
  * wait since the last call (FXB_ERR_DEVICE_TIMEOUT) — the counterpart of the launch error
  * string formatted at src/backend/cuda/kernels.rs:33. */
 int fxb_check_device_status(fxb_handle_t h, fxb_stream_t stream);
+/* Self-test of that convention (no reference counterpart): launches one warp that waits, for at most
+ * `limit_cycles` SM cycles (1..1e8), on a barrier nobody arrives on.  The wait gives up, the kernel
+ * returns normally, and the next fxb_check_device_status reports FXB_ERR_DEVICE_TIMEOUT with tag 99
+ * and clears it; the handle stays usable.  Nothing faults, traps or spins without a bound. */
+int fxb_selftest_bounded_wait(fxb_handle_t h, int64_t limit_cycles, fxb_stream_t stream);
 int fxb_version(void);
 /* Number of kernels this handle has launched so far (for launch accounting in benchmarks). */
 uint64_t fxb_launch_count(fxb_handle_t h);
@@ -139,9 +145,10 @@ int fxb_conv2d_bias_act_fwd_f64(fxb_handle_t h, const double* X, const double* W
                                 fxb_stream_t stream);
 /* Workspace of the f32 forward / input-gradient kernels (0 for f64).  With a 256-byte aligned workspace of
  * at least this size the image and the filter are first rewritten once into TF32 hi / lo arrays with
- * 4 channels per pixel contiguous, and the contraction kernel fills its operand tiles with 16-byte
- * cp.async copies; with workspace == NULL (or too small) the operands are gathered and split on the
- * fly inside the kernel.  Both ways give the same values. */
+ * 4 channels per pixel contiguous (one plane per stride class), and the contraction kernel's operand
+ * tiles are filled by the tensor-map copy engine (cp.async.bulk.tensor), or by 16-byte cp.async copies
+ * for shapes a tensor map cannot describe; with workspace == NULL (or too small) the operands are
+ * gathered and split on the fly inside the kernel.  All ways give the same values. */
 size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
 /* Runs only the operand pre-pass of fxb_conv2d_forward_f32 (image and filter rewritten as TF32 hi / lo
  * arrays in the workspace) and stops before the contraction kernel, so that the two parts can be timed
@@ -149,6 +156,11 @@ size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d
  * pre-pass (C*R*S <= 32, or shapes the tensor-map engine cannot describe). */
 int fxb_conv2d_fprop_prepass_f32(fxb_handle_t h, const float* X, const float* W, const fxb_conv2d_desc* d,
                                  void* workspace, size_t workspace_bytes, fxb_stream_t stream);
+/* The other half: only the contraction kernel of fxb_conv2d_bias_act_fwd_f32, reading the operands that
+ * fxb_conv2d_fprop_prepass_f32 left in `workspace` for the same descriptor (so the kernel can be timed
+ * on its own).  No reference counterpart.  Same FXB_ERR_UNSUPPORTED cases as the pre-pass. */
+int fxb_conv2d_fprop_main_f32(fxb_handle_t h, const float* bias, float* Y, const fxb_conv2d_desc* d, int act,
+                              void* workspace, size_t workspace_bytes, fxb_stream_t stream);
 size_t fxb_conv2d_dgrad_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
 
 /* ---- conv2d input gradient: CudaOps::deconv2d (src/backend/cuda/ops.rs:1458-1539), kernel
@@ -220,7 +232,8 @@ int fxb_bias_add_f64(fxb_handle_t h, double* y, const double* bias, int64_t oute
 /* ---- reductions: CudaOps::sum_axes / sum_all (src/backend/cuda/ops.rs:653-697, :2171-2284),
  *      kernels `reduce_sum_axes`, `reduce_sum_all` (kernels/reduction.cu:9-84).  `axes` lists the
  *      reduced axes (any order); the output holds the kept axes in order (keep_dims only
- *      changes the shape on the caller's side).  Up to 4-D inputs; two-stage and deterministic.
+ *      changes the shape on the caller's side).  Up to 8-D inputs; two-stage and deterministic
+ *      (more than two separate runs of reduced axes take a second round through the workspace).
  *      The partial sums of stage one live in `workspace`. ---- */
 int fxb_sum_axes_f32(fxb_handle_t h, const float* x, const int64_t* shape, int ndim, const int* axes, int naxes,
                      float* out, void* workspace, size_t workspace_bytes, fxb_stream_t stream);
@@ -235,15 +248,79 @@ size_t fxb_sum_axes_workspace_bytes(fxb_handle_t h, const int64_t* shape, int nd
  * synchronises the device and may fail for the same reason).  The stage-one partial sums live in a
  * 512 KiB device array that is part of the library image (held by every GPU that loads the library
  * until exit); nothing is allocated or freed.  Reductions whose partial sums exceed 512 KiB return
- * FXB_ERR_WORKSPACE.  The first call on a device resolves the array's address and should come
- * before any stream capture.  All calls on a device share the array: calls that overlap on the
- * GPU race; nothing needs clearing between calls.  Results are bit-identical to fxb_sum_axes_f32. */
+ * FXB_ERR_WORKSPACE.  fxb_create resolves the array's device address (cudaGetSymbolAddress with the
+ * handle's device current), so a call here never reaches the module loader; create the handle before
+ * any stream capture.  All calls on a device share the array: calls that overlap on the GPU race;
+ * nothing needs clearing between calls.  Results are bit-identical to fxb_sum_axes_f32. */
 int fxb_sum_axes_static_scratch_f32(fxb_handle_t h, const float* x, const int64_t* shape, int ndim, const int* axes,
                                     int naxes, float* out, fxb_stream_t stream);
 int fxb_sum_all_f32(fxb_handle_t h, const float* x, int64_t n, float* out, void* workspace, size_t workspace_bytes,
                     fxb_stream_t stream);
 int fxb_sum_all_f64(fxb_handle_t h, const double* x, int64_t n, double* out, void* workspace,
                     size_t workspace_bytes, fxb_stream_t stream);
+
+/* ---- layout: CudaOps::materialize (src/backend/cuda/ops.rs:175-214), kernel `materialize[_f64]`
+ *      (kernels/materialize.cu:25-46): out (contiguous, `shape`) = the view of `in` with element
+ *      strides `strides` (0 = a broadcast dimension).  Shape and strides travel in the launch
+ *      parameters (the reference copies both arrays to the device on every call).  Up to 8-D,
+ *      fewer than 2^31 elements.  Pure data movement: bit-exact. ---- */
+int fxb_materialize_f32(fxb_handle_t h, const float* in, float* out, const int64_t* shape, const int64_t* strides,
+                        int ndim, fxb_stream_t stream);
+int fxb_materialize_f64(fxb_handle_t h, const double* in, double* out, const int64_t* shape, const int64_t* strides,
+                        int ndim, fxb_stream_t stream);
+/* Transpose as its own op: Tensor::transpose + materialize (src/ops/matrix.rs:69-110,
+ * src/backend/storage/cuda.rs:826-857).  `in` is contiguous with `shape`; out[i0..] = in permuted so
+ * that output axis i is input axis axes[i]; axes == NULL reverses all axes (the matrix transpose). */
+int fxb_transpose_f32(fxb_handle_t h, const float* in, float* out, const int64_t* shape, int ndim, const int* axes,
+                      fxb_stream_t stream);
+int fxb_transpose_f64(fxb_handle_t h, const double* in, double* out, const int64_t* shape, int ndim, const int* axes,
+                      fxb_stream_t stream);
+/* broadcast_to + materialize (src/backend/storage/cuda.rs:795-803, src/ops/reshape.rs:26-41): shapes are
+ * aligned at the last axis; an input extent must equal the target's or be 1. */
+int fxb_broadcast_to_f32(fxb_handle_t h, const float* in, const int64_t* in_shape, int in_ndim, float* out,
+                         const int64_t* out_shape, int out_ndim, fxb_stream_t stream);
+int fxb_broadcast_to_f64(fxb_handle_t h, const double* in, const int64_t* in_shape, int in_ndim, double* out,
+                         const int64_t* out_shape, int out_ndim, fxb_stream_t stream);
+
+/* ---- batch normalisation: BatchNorm::forward (src/nn/layers/norm.rs:214-331) and the gradients its
+ *      graph ops chain (Mean, Sub, Mul, Sqrt, Div, BroadcastTo: src/ops/reduction.rs:156-196,
+ *      src/ops/basic.rs:187-263, src/ops/unary.rs:123-143), fused.  x is [N, C, P] with P = H*W
+ *      (P = 1 for a [N, F] input).  Training: batch_mean / batch_var (biased, as the reference
+ *      computes it) are outputs and the running statistics, when given, are updated in place with
+ *      running = (1 - momentum) * running + momentum * batch (norm.rs:126-163).  Inference
+ *      (training == 0): the running statistics normalise, no workspace is needed.
+ *      y = act(((x - mean) / sqrt(var + eps)) * gamma + beta); gamma / beta may be NULL (1 / 0).
+ *      Backward: dZ = dY * act'(Y); dbeta = sum dZ, dgamma = sum dZ * xhat,
+ *      dX = (gamma / std) * (dZ - dbeta / M - xhat * dgamma / M); dX may be NULL. ---- */
+int fxb_batch_norm_fwd_f32(fxb_handle_t h, const float* x, const float* gamma, const float* beta, float* y,
+                           float* batch_mean, float* batch_var, float* running_mean, float* running_var, int64_t N,
+                           int64_t C, int64_t P, double eps, double momentum, int training, int act, void* workspace,
+                           size_t workspace_bytes, fxb_stream_t stream);
+int fxb_batch_norm_fwd_f64(fxb_handle_t h, const double* x, const double* gamma, const double* beta, double* y,
+                           double* batch_mean, double* batch_var, double* running_mean, double* running_var, int64_t N,
+                           int64_t C, int64_t P, double eps, double momentum, int training, int act, void* workspace,
+                           size_t workspace_bytes, fxb_stream_t stream);
+int fxb_batch_norm_bwd_f32(fxb_handle_t h, const float* x, const float* dy, const float* y, const float* gamma,
+                           const float* batch_mean, const float* batch_var, float* dx, float* dgamma, float* dbeta,
+                           int64_t N, int64_t C, int64_t P, double eps, int act, void* workspace, size_t workspace_bytes,
+                           fxb_stream_t stream);
+int fxb_batch_norm_bwd_f64(fxb_handle_t h, const double* x, const double* dy, const double* y, const double* gamma,
+                           const double* batch_mean, const double* batch_var, double* dx, double* dgamma, double* dbeta,
+                           int64_t N, int64_t C, int64_t P, double eps, int act, void* workspace, size_t workspace_bytes,
+                           fxb_stream_t stream);
+size_t fxb_batch_norm_workspace_bytes(fxb_handle_t h, int64_t N, int64_t C, int64_t P, size_t elem_size);
+
+/* ---- global average pooling: GlobalAvgPool2d::forward = Mean over axes [2, 3]
+ *      (src/nn/layers/pooling.rs:604-619) and Mean::gradient (src/ops/reduction.rs:170-196):
+ *      y[N, C] = sum over H*W * (1 / (H*W));  dx[n, c, :, :] = dy[n, c] * (1 / (H*W)). ---- */
+int fxb_global_avg_pool_fwd_f32(fxb_handle_t h, const float* x, float* y, int64_t N, int64_t C, int64_t H, int64_t W,
+                                fxb_stream_t stream);
+int fxb_global_avg_pool_fwd_f64(fxb_handle_t h, const double* x, double* y, int64_t N, int64_t C, int64_t H, int64_t W,
+                                fxb_stream_t stream);
+int fxb_global_avg_pool_bwd_f32(fxb_handle_t h, const float* dy, float* dx, int64_t N, int64_t C, int64_t H, int64_t W,
+                                fxb_stream_t stream);
+int fxb_global_avg_pool_bwd_f64(fxb_handle_t h, const double* dy, double* dx, int64_t N, int64_t C, int64_t H, int64_t W,
+                                fxb_stream_t stream);
 
 /* ---- loss and optimizers (the callers right after / before the path inside a train step).
  *      Softmax cross-entropy with mean reduction, forward and gradient in one kernel:

@@ -202,6 +202,121 @@ def adam_step(p, g, m, v, step, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.0):
 
 
 # ----------------------------------------------------------------------------------------------
+# Layout ops, batch normalisation and global average pooling: numpy restatements (pure data
+# movement, or the reference's graph ops applied one after the other in the tensor's own dtype).
+def materialize(data, shape, strides):
+    """Contiguous copy of the view (shape, element strides; 0 = broadcast) of the flat array `data`:
+    kernels/materialize.cu:25-46 (output index -> coordinates -> strided input index)."""
+    data = np.asarray(data).ravel()
+    idx = np.zeros(tuple(shape), np.int64)
+    for ax, (n, st) in enumerate(zip(shape, strides)):
+        sh = [1] * len(shape)
+        sh[ax] = n
+        idx = idx + (np.arange(n, dtype=np.int64) * st).reshape(sh)
+    return data[idx]
+
+
+def transpose(x, axes=None):
+    """CPUStorage::transpose (src/backend/storage/cpu.rs:543-562): permuted axes, owned copy;
+    axes=None reverses all axes."""
+    return np.ascontiguousarray(np.transpose(np.asarray(x), axes))
+
+
+def broadcast_to(x, shape):
+    """CPUStorage::broadcast_to (src/backend/storage/cpu.rs:510-541): shapes aligned at the last axis,
+    an extent must equal the target's or be 1."""
+    x = np.asarray(x)
+    if len(shape) < x.ndim:
+        raise ValueError("Cannot broadcast to smaller number of dimensions")
+    off = len(shape) - x.ndim
+    for i, (c, t) in enumerate(zip(x.shape, shape[off:])):
+        if c != 1 and c != t:
+            raise ValueError(f"Cannot broadcast dimension {i} from size {c} to size {t}")
+    return np.ascontiguousarray(np.broadcast_to(x, shape))
+
+
+def _bn_axes(x):
+    return [0, 2, 3] if x.ndim == 4 else [0]
+
+
+def _bc(v, x):
+    """reshape_and_broadcast (src/nn/layers/utils.rs:6-42): [C] -> [1, C, 1, 1] (or [1, C])."""
+    return v.reshape([1, -1] + [1] * (x.ndim - 2))
+
+
+def mean_axes(x, axes):
+    """CPUStorage::mean (src/backend/storage/cpu.rs:1193-1221): sum, then times 1/count."""
+    count = int(np.prod([x.shape[a] for a in axes]))
+    return sum_axes(x, axes) * x.dtype.type(1.0 / count)
+
+
+def batch_norm_fwd(x, gamma, beta, eps=1e-5, running_mean=None, running_var=None, momentum=0.1, training=True):
+    """BatchNorm::apply_training_batch_norm / apply_inference_batch_norm / finish_normalization
+    (src/nn/layers/norm.rs:190-331), op by op.  Training returns (y, batch_mean, batch_var) and
+    updates running_mean / running_var in place (norm.rs:126-163)."""
+    x = _c(x)
+    dt = x.dtype.type
+    axes = _bn_axes(x)
+    if training:
+        mean = mean_axes(x, axes)
+        centered = x - _bc(mean, x)
+        var = mean_axes(centered * centered, axes)
+        if running_mean is not None:
+            running_mean[...] = running_mean * dt(1.0 - momentum) + mean * dt(momentum)
+            running_var[...] = running_var * dt(1.0 - momentum) + var * dt(momentum)
+    else:
+        mean, var = running_mean, running_var
+        centered = x - _bc(mean, x)
+    std = np.sqrt(_bc(var, x) + dt(eps))
+    normalized = centered / std
+    y = normalized * _bc(_c(gamma, x.dtype), x) + _bc(_c(beta, x.dtype), x)
+    return (y, mean, var) if training else y
+
+
+def batch_norm_bwd(x, dy, gamma, mean, var, eps=1e-5):
+    """Gradients of the training-mode graph above, chained rule by rule: Add / Mul / Div
+    (src/ops/basic.rs:95-115, :187-263), Sqrt (src/ops/unary.rs:123-143), AddScalar, BroadcastTo
+    (src/ops/reshape.rs:82-99), Mean (src/ops/reduction.rs:170-196), Sub.  Returns (dx, dgamma, dbeta)."""
+    x, dy = _c(x), _c(dy, x.dtype)
+    dt = x.dtype.type
+    axes = _bn_axes(x)
+    m = int(np.prod([x.shape[a] for a in axes]))
+    inv_m = dt(1.0 / m)
+    centered = x - _bc(mean, x)
+    std = np.sqrt(np.broadcast_to(_bc(var, x), x.shape) + dt(eps))
+    normalized = centered / std
+    gb = _bc(_c(gamma, x.dtype), x)
+    dbeta = sum_axes(dy, axes)                       # Add -> BroadcastTo::gradient
+    dgamma = sum_axes(dy * normalized, axes)         # Mul
+    d_norm = dy * gb
+    d_centered = d_norm / std                        # Div, first input
+    d_std = d_norm * (-(normalized / std))           # Div, second input: grad * -(out / b)
+    d_vpe = d_std / (std * dt(2.0))                  # Sqrt: grad / (2 * out)
+    d_var = sum_axes(_c(d_vpe), axes)                # BroadcastTo::gradient of the variance
+    d_sq = np.broadcast_to(_bc(d_var * inv_m, x), x.shape)  # Mean::gradient
+    d_centered = d_centered + d_sq * centered        # Mul(centered, centered): both inputs accumulate
+    d_centered = d_centered + d_sq * centered
+    d_mean = sum_axes(_c(-d_centered), axes)         # Sub, second input -> BroadcastTo::gradient
+    dx = d_centered + np.broadcast_to(_bc(d_mean * inv_m, x), x.shape)
+    return _c(dx), dgamma, dbeta
+
+
+def global_avg_pool_fwd(x, flatten=True):
+    """GlobalAvgPool2d::forward (src/nn/layers/pooling.rs:604-619): Mean over axes [2, 3]."""
+    x = _c(x)
+    y = mean_axes(x, [2, 3])
+    return y if flatten else y.reshape(x.shape[0], x.shape[1], 1, 1)
+
+
+def global_avg_pool_bwd(dy, x_shape):
+    """Mean::gradient (src/ops/reduction.rs:170-196): grad * (1/count), broadcast to the input shape."""
+    dy = _c(dy)
+    n, c, h, w = x_shape
+    scaled = dy.reshape(n, c) * dy.dtype.type(1.0 / (h * w))
+    return np.ascontiguousarray(np.broadcast_to(scaled.reshape(n, c, 1, 1), x_shape))
+
+
+# ----------------------------------------------------------------------------------------------
 # Sequential network train step, composed like the reference graph.
 # layers: list of dicts
 #   {"kind": "conv", "stride": s, "pad": p, "act": ACT_*}   params W [K,C,R,S], b [K]

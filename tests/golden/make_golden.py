@@ -129,6 +129,23 @@ def main(ref):
     a = arrays(body(sgd, "test_sgd_basic_step"))
     G["test_sgd_basic_step"] = {"source": "src/nn/optim/sgd.rs::test_sgd_basic_step", "param": a[0], "grad": a[2],
                                 "lr": 0.1, "expected": [1.9], "tol": 1e-6}
+    a = arrays(body(ops, "test_global_avgpool2d_forward"))
+    G["test_global_avgpool2d_forward"] = {"source": "src/ops/mod.rs::test_global_avgpool2d_forward", "input": a[0],
+                                          "x_shape": [1, 1, 4, 4], "y_shape": [int(v) for v in a[2]], "expected": a[1], "tol": 1e-4}
+    cops = open(os.path.join(ref, "src/backend/cuda/ops.rs")).read()
+    b = body(cops, "test_bias_broadcasting")
+    bias = [float(re.sub(r"f32|f64", "", str(re.findall(r"let bias_data = vec!\[(" + NUM + r")\]", b)[0])))]
+    target = [int(v) for v in re.findall(r"broadcast_to\(&mut bias_tensor, &\[(\d+)\]\)", b)]
+    rep = re.search(r"vec!\[(" + NUM + r");\s*(\d+)\]", b)
+    G["test_bias_broadcasting"] = {"source": "src/backend/cuda/ops.rs::test_bias_broadcasting", "input": bias, "in_shape": [1],
+                                   "target_shape": target,
+                                   "expected": [float(re.sub(r"f32|f64", "", rep.group(1)))] * int(rep.group(2)), "tol": 1e-6}
+    b = body(ten, "test_transpose_operation")
+    G["test_transpose_operation"] = {"source": "src/backend/tensor.rs::test_transpose_operation", "input": arrays(b)[0],
+                                     "shape": [2, 3], "expected_shape": [3, 2]}
+    b = body(ten, "test_broadcast_to")
+    G["test_broadcast_to"] = {"source": "src/backend/tensor.rs::test_broadcast_to", "input": arrays(b)[0], "in_shape": [2],
+                              "target_shape": [3, 2]}
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_known_answers.json")
     with open(out, "w") as f:
         json.dump(G, f, indent=1)

@@ -153,3 +153,65 @@ def test_train_step_composition_matches_autograd(oracle):
     assert abs(loss - lt.item()) < 1e-12
     for (dw, db), (wt, bt) in zip(grads, tp):
         assert np.abs(dw - wt.grad.numpy()).max() < 1e-12 and np.abs(db - bt.grad.numpy()).max() < 1e-12
+
+
+def test_golden_layout_and_pooling(golden, oracle):
+    g = golden["test_global_avgpool2d_forward"]
+    x = np.array(g["input"], np.float32).reshape(g["x_shape"])
+    y = oracle.global_avg_pool_fwd(x, flatten=False)
+    assert list(y.shape) == g["y_shape"] and np.abs(y.ravel() - np.array(g["expected"], np.float32)).max() <= g["tol"]
+    g = golden["test_bias_broadcasting"]
+    b = oracle.broadcast_to(np.array(g["input"], np.float32).reshape(g["in_shape"]), g["target_shape"])
+    assert np.abs(b - np.array(g["expected"], np.float32)).max() <= g["tol"]
+    # the same through the strided materialise restatement (stride 0 on the broadcast axis)
+    assert np.array_equal(oracle.materialize(np.array(g["input"], np.float32), g["target_shape"], [0]), b)
+    g = golden["matrix_transpose"]
+    a = np.array(g["input"], np.float32).reshape(g["rows"], g["cols"])
+    assert oracle.transpose(a).ravel().tolist() == g["expected"]
+    assert np.array_equal(oracle.materialize(a, (3, 2), (1, 3)), a.T)
+    g = golden["test_transpose_operation"]
+    assert list(oracle.transpose(np.array(g["input"], np.float32).reshape(g["shape"])).shape) == g["expected_shape"]
+    g = golden["test_broadcast_to"]
+    assert list(oracle.broadcast_to(np.array(g["input"], np.float32), g["target_shape"]).shape) == g["target_shape"]
+    with pytest.raises(ValueError, match="Cannot broadcast dimension"):
+        oracle.broadcast_to(np.zeros((3,)), (2, 2))
+
+
+@pytest.mark.parametrize("shape", [(6, 5, 4, 3), (16, 7)])
+def test_batch_norm_matches_independent_autograd(oracle, shape):
+    """The reference holds no value test for BatchNorm; the op-by-op restatement is pinned to torch's f64
+    batch norm (biased variance in the normalisation) and to the running-statistics rule of norm.rs:126-163."""
+    rng = np.random.default_rng(13)
+    x = rng.standard_normal(shape) * 2 + 0.5
+    C = shape[1]
+    gamma, beta = rng.standard_normal(C), rng.standard_normal(C)
+    rm, rv = rng.standard_normal(C), rng.random(C) + 0.5
+    rm0, rv0 = rm.copy(), rv.copy()
+    y, mean, var = oracle.batch_norm_fwd(x, gamma, beta, 1e-3, rm, rv, 0.1, training=True)
+    xt = torch.tensor(x, requires_grad=True)
+    gt, bt = torch.tensor(gamma, requires_grad=True), torch.tensor(beta, requires_grad=True)
+    yt = F.batch_norm(xt, None, None, gt, bt, training=True, eps=1e-3)
+    assert np.abs(y - yt.detach().numpy()).max() < 1e-12
+    axes = (0, 2, 3) if len(shape) == 4 else (0,)
+    assert np.abs(mean - x.mean(axes)).max() < 1e-12 and np.abs(var - x.var(axes)).max() < 1e-12
+    assert np.abs(rm - (0.9 * rm0 + 0.1 * mean)).max() < 1e-12 and np.abs(rv - (0.9 * rv0 + 0.1 * var)).max() < 1e-12
+    dy = rng.standard_normal(shape)
+    yt.backward(torch.tensor(dy))
+    dx, dg, db = oracle.batch_norm_bwd(x, dy, gamma, mean, var, 1e-3)
+    assert np.abs(dx - xt.grad.numpy()).max() < 1e-12
+    assert np.abs(dg - gt.grad.numpy()).max() < 1e-11 and np.abs(db - bt.grad.numpy()).max() < 1e-11
+    # inference: the running statistics normalise
+    yi = oracle.batch_norm_fwd(x, gamma, beta, 1e-3, rm, rv, training=False)
+    yti = F.batch_norm(torch.tensor(x), torch.tensor(rm), torch.tensor(rv), torch.tensor(gamma), torch.tensor(beta), training=False, eps=1e-3)
+    assert np.abs(yi - yti.numpy()).max() < 1e-12
+
+
+def test_global_avg_pool_matches_independent_autograd(oracle):
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((3, 5, 7, 6))
+    xt = torch.tensor(x, requires_grad=True)
+    yt = xt.mean((2, 3))
+    dy = rng.standard_normal((3, 5))
+    yt.backward(torch.tensor(dy))
+    assert np.abs(oracle.global_avg_pool_fwd(x) - yt.detach().numpy()).max() < 1e-13
+    assert np.abs(oracle.global_avg_pool_bwd(dy, x.shape) - xt.grad.numpy()).max() < 1e-13
