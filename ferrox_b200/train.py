@@ -212,6 +212,11 @@ class Trainer:
                 works.append(self._allreduce(net.grads))
         for w in works:
             w.wait()
+        self._optimizer_step()
+        return net.loss_slot
+
+    def _optimizer_step(self):
+        net, ops = self.net, self.ops
         self.step_count += 1
         g = net.grads[: net.nparams]
         if self.optimizer == "adam":
@@ -221,7 +226,43 @@ class Trainer:
         else:
             ops.sgd_step_(net.params, g, self.mom, lr=self.lr, momentum=self.opt_kw.get("momentum", 0.0),
                           weight_decay=self.opt_kw.get("weight_decay", 0.0), nesterov=self.opt_kw.get("nesterov", False))
-        return net.loss_slot
+
+    def step_with_marks(self, x, targets):
+        """The same step as step(), one parameter layer per backward call, with a CUDA event and a host
+        timestamp recorded at the start of every phase.  Returns [(phase name, event, host seconds)], the
+        last entry marking the end; the time between two events is the phase's time on the compute stream
+        (for "allreduce_wait": the part of the all-reduces that backward did not hide)."""
+        import time
+        net = self.net
+        n = net.n_param_layers
+        marks = []
+
+        def mark(name):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            marks.append((name, e, time.perf_counter()))
+
+        mark("forward")
+        net.forward(x)
+        mark("loss")
+        net.loss(targets, 1.0 / self.world)
+        works = []
+        for pi in range(n - 1, -1, -1):
+            mark(f"backward_layer{pi}")
+            net.backward_range(x, pi, pi)
+            if self.world > 1 and self.split_layer > 0 and pi == self.split_layer:
+                mark("allreduce_tail_issue")
+                works.append(self._allreduce(net.grads[self.split_off:]))
+        if self.world > 1:
+            mark("allreduce_head_issue")
+            works.append(self._allreduce(net.grads[: self.split_off] if self.split_layer > 0 else net.grads))
+        mark("allreduce_wait")
+        for w in works:
+            w.wait()
+        mark("optimizer")
+        self._optimizer_step()
+        mark("end")
+        return marks
 
     def loss_value(self):
         """Global mean loss of the last step (one device-to-host read).  This is the step's only

@@ -6,8 +6,9 @@
 //
 // The reference's contractions go through ndarray 0.16.1 `ArrayBase::dot`, which calls
 // matrixmultiply 0.3.10 (Cargo.lock:163-174); neither crate is vendored in the reference, so
-// the GEMM here is a plain row-major triple loop (any f32 summation order is inside the
-// parity tolerance).  Everything else follows the reference line by line; each function cites
+// the GEMM here is a plain register-blocked triple loop that the compiler vectorises (any f32
+// summation order is inside the parity tolerance; a hand-tuned SIMD micro-kernel like
+// matrixmultiply's is still somewhat faster).  Everything else follows the reference line by line; each function cites
 // the file:line it restates (paths relative to the reference repository root).
 //
 // Parity pinning: checked against the reference's own known-answer tests (tests/golden/),
@@ -36,11 +37,42 @@ namespace {
 // src/backend/storage/extensions/convolutions.rs:256, :296, :332.
 template <typename T>
 void gemm_nn(const T* A, const T* B, T* C, int64_t M, int64_t N, int64_t K) {
+    // Register-blocked: a 4 x 32 block of C is accumulated over one k-panel in local variables (the
+    // compiler keeps them in vector registers), so every loaded B value feeds four rows.  Per output
+    // element the products are added in ascending k inside a panel and the panels in ascending order.
     std::fill(C, C + M * N, T(0));
-    const int64_t KB = 256;  // k-panel so a B panel stays cache resident
+    constexpr int64_t KB = 256, MR = 4, NR = 32;
     for (int64_t k0 = 0; k0 < K; k0 += KB) {
         const int64_t k1 = std::min(K, k0 + KB);
-        for (int64_t i = 0; i < M; ++i) {
+        int64_t i = 0;
+        for (; i + MR <= M; i += MR) {
+            int64_t j = 0;
+            for (; j + NR <= N; j += NR) {
+                T acc[MR][NR];
+                for (int64_t r = 0; r < MR; ++r)
+                    for (int64_t c = 0; c < NR; ++c) acc[r][c] = T(0);
+                for (int64_t k = k0; k < k1; ++k) {
+                    const T* b = B + k * N + j;
+                    const T a0 = A[(i + 0) * K + k], a1 = A[(i + 1) * K + k], a2 = A[(i + 2) * K + k], a3 = A[(i + 3) * K + k];
+                    for (int64_t c = 0; c < NR; ++c) {
+                        const T bv = b[c];
+                        acc[0][c] += a0 * bv;
+                        acc[1][c] += a1 * bv;
+                        acc[2][c] += a2 * bv;
+                        acc[3][c] += a3 * bv;
+                    }
+                }
+                for (int64_t r = 0; r < MR; ++r)
+                    for (int64_t c = 0; c < NR; ++c) C[(i + r) * N + j + c] += acc[r][c];
+            }
+            for (; j < N; ++j)
+                for (int64_t r = 0; r < MR; ++r) {
+                    T s = T(0);
+                    for (int64_t k = k0; k < k1; ++k) s += A[(i + r) * K + k] * B[k * N + j];
+                    C[(i + r) * N + j] += s;
+                }
+        }
+        for (; i < M; ++i) {
             T* c = C + i * N;
             for (int64_t k = k0; k < k1; ++k) {
                 const T a = A[i * K + k];
