@@ -54,6 +54,7 @@ def _sigs(real):
         "conv2d_dgrad_act": (I, [H, _P, _P, _P, _P, _DP, I, _P, SZ, S]),
         "cross_correlation2d": (I, [H, _P, _P, _P, _DP, _P, SZ, S]),
         "conv2d_wgrad_bias_act": (I, [H, _P, _P, _P, _P, _P, _DP, I, _P, SZ, S]),
+        "conv2d_backward": (I, [H, _P, _P, _P, _P, _P, _P, _P, _DP, I, _P, SZ, _P, S]),
         "act_fwd": (I, [H, _P, _P, I64, I, S]),
         "act_bwd": (I, [H, _P, _P, _P, I64, I, S]),
         "add": (I, [H, _P, _P, _P, I64, S]),
@@ -95,6 +96,10 @@ _COMMON = {
     "fxb_conv2d_fprop_prepass_f32": (c_int, [c_void_p, c_void_p, c_void_p, _DP, c_void_p, c_size_t, c_void_p]),
     "fxb_conv2d_fprop_main_f32": (c_int, [c_void_p, c_void_p, c_void_p, _DP, c_int, c_void_p, c_size_t, c_void_p]),
     "fxb_conv2d_dgrad_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
+    "fxb_conv2d_backward_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
+    "fxb_conv2d_packed_input_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
+    "fxb_conv2d_bias_act_fwd_packing_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, _DP, c_int, c_void_p, c_size_t,
+                                                    c_void_p, c_size_t, POINTER(c_int), c_void_p]),
     "fxb_batch_norm_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
     "fxb_sum_axes_workspace_bytes": (c_size_t, [c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_size_t]),
     "fxb_sum_axes_static_scratch_f32": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_void_p,

@@ -165,53 +165,133 @@ __global__ void __launch_bounds__(256) split_filter_chunk_major_kernel(const flo
 }
 
 // ------------------------------------------------------------------------------------------
-// Pre-pass kernels of the tensor-map filter-gradient path.
+// Pre-pass kernels of the tensor-map filter-gradient path (and, fused, of the input-gradient path).
 //
-// dZ = dY * act'(Y), NCHW -> chunk-major DZ[g][o][4] (hi and lo), g = n*PQ + pixel quad, rows padded
-// with zeros to `Kp` output channels.  The same pass produces the bias gradient deterministically:
-// block (bx, by) adds the values of its GB chunks for its 64 output channels and writes
-// dbpart[bx][o]; the partial rows are added in order by splitk_reduce_kernel.
-constexpr int DZ_GB = 64;  // chunks per block
-__global__ void __launch_bounds__(256) split_dz_chunk_major_kernel(const float* __restrict__ dy, const float* __restrict__ yact,
-                                                                   float* __restrict__ hi, float* __restrict__ lo,
-                                                                   float* __restrict__ dbpart, int K, int Kp, int PQ, int64_t G,
-                                                                   int act, int sig_math) {
-    __shared__ float red[4][64];
-    const int ol = threadIdx.x & 63, gl = threadIdx.x >> 6;
-    const int o = blockIdx.y * 64 + ol;
-    const int64_t g0 = (int64_t)blockIdx.x * DZ_GB;
-    float sum = 0.f;
-    if (o < Kp) {
-        for (int it = 0; it < DZ_GB / 4; ++it) {
-            const int64_t g = g0 + it * 4 + gl;
-            if (g >= G) break;
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (o < K) {
-                const int64_t n = g / PQ;
-                const int pq = (int)(g - n * PQ);
-                const int64_t src = ((n * K + o) * PQ + pq) * 4;
-                v = __ldg(reinterpret_cast<const float4*>(dy + src));
-                if (yact) {
-                    const float4 a = __ldg(reinterpret_cast<const float4*>(yact + src));
-                    v.x *= act_grad_factor<float>(a.x, act, sig_math);
-                    v.y *= act_grad_factor<float>(a.y, act, sig_math);
-                    v.z *= act_grad_factor<float>(a.z, act, sig_math);
-                    v.w *= act_grad_factor<float>(a.w, act, sig_math);
-                }
-                sum += (v.x + v.y) + (v.z + v.w);
-            }
-            uint4 h;
-            h.x = cvt_tf32_rna(v.x); h.y = cvt_tf32_rna(v.y); h.z = cvt_tf32_rna(v.z); h.w = cvt_tf32_rna(v.w);
-            const int64_t dst = (g * Kp + o) * 4;
-            *reinterpret_cast<uint4*>(hi + dst) = h;
-            *reinterpret_cast<float4*>(lo + dst) = make_float4(v.x - __uint_as_float(h.x), v.y - __uint_as_float(h.y),
-                                                               v.z - __uint_as_float(h.z), v.w - __uint_as_float(h.w));
+// dZ = dY * act'(Y), NCHW -> DZN[g][p][o][4] (hi and lo): the values of images 4g..4g+3 at pixel p and
+// output channel o, rows padded with zeros to `Kp` channels, images beyond N are zeros.  With `slab_hi`
+// the same pass also writes the channel slabs S[o/4][n][p][4] that the input-gradient kernel reads, and
+// with `dbpart` the bias gradient, deterministically: block (bx, by, g) adds its 4 x 32 values of each of its
+// 32 output channels and writes dbpart[g * gridDim.x + bx][o]; partial_rows_sum_kernel adds the rows in order.
+// Block = 4 images x 32 channels x 32 pixels through shared memory: reads coalesced along the pixels,
+// writes coalesced along the channels (DZN) and along the pixels (slabs).
+__device__ __forceinline__ void store_split4(float* hi, float* lo, int64_t o, float v0, float v1, float v2, float v3) {
+    uint4 h;
+    h.x = cvt_tf32_rna(v0); h.y = cvt_tf32_rna(v1); h.z = cvt_tf32_rna(v2); h.w = cvt_tf32_rna(v3);
+    *reinterpret_cast<uint4*>(hi + o) = h;
+    *reinterpret_cast<float4*>(lo + o) = make_float4(v0 - __uint_as_float(h.x), v1 - __uint_as_float(h.y),
+                                                     v2 - __uint_as_float(h.z), v3 - __uint_as_float(h.w));
+}
+__global__ void __launch_bounds__(256) pack_dz_kernel(const float* __restrict__ dy, const float* __restrict__ yact,
+                                                      float* __restrict__ dzn_hi, float* __restrict__ dzn_lo,
+                                                      float* __restrict__ slab_hi, float* __restrict__ slab_lo,
+                                                      float* __restrict__ dbpart, int N, int K, int Kp, int P, int act,
+                                                      int sig_math) {
+    __shared__ float t[4][32][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p0 = blockIdx.x * 32, o0 = blockIdx.y * 32, g = blockIdx.z;
+    for (int q = warp; q < 128; q += 8) {
+        const int n4 = q >> 5, ol = q & 31;
+        const int n = 4 * g + n4, o = o0 + ol, p = p0 + lane;
+        float v = 0.f;
+        if (n < N && o < K && p < P) {
+            const int64_t src = ((int64_t)n * K + o) * P + p;
+            v = __ldg(dy + src);
+            if (yact) v *= act_grad_factor<float>(__ldg(yact + src), act, sig_math);
+        }
+        t[n4][ol][lane] = v;
+    }
+    __syncthreads();
+    if (dbpart != nullptr && warp == 0 && o0 + lane < K) {
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        for (int p = 0; p < 32; ++p) {
+            s0 += t[0][lane][p]; s1 += t[1][lane][p]; s2 += t[2][lane][p]; s3 += t[3][lane][p];
+        }
+        dbpart[((int64_t)g * gridDim.x + blockIdx.x) * K + o0 + lane] = (s0 + s1) + (s2 + s3);
+    }
+    for (int i = threadIdx.x; i < 1024; i += 256) {
+        const int ol = i & 31, pl = i >> 5;
+        const int o = o0 + ol, p = p0 + pl;
+        if (o < Kp && p < P)
+            store_split4(dzn_hi, dzn_lo, (((int64_t)g * P + p) * Kp + o) * 4, t[0][ol][pl], t[1][ol][pl], t[2][ol][pl], t[3][ol][pl]);
+    }
+    if (slab_hi != nullptr) {
+        const int K4 = (K + 3) >> 2;
+        for (int i = threadIdx.x; i < 1024; i += 256) {
+            const int pl = i & 31, rest = i >> 5;
+            const int n4 = rest >> 3, q = rest & 7;
+            const int n = 4 * g + n4, p = p0 + pl, k4 = (o0 >> 2) + q;
+            if (n < N && p < P && k4 < K4)
+                store_split4(slab_hi, slab_lo, (((int64_t)k4 * N + n) * P + p) * 4, t[n4][4 * q][pl], t[n4][4 * q + 1][pl],
+                             t[n4][4 * q + 2][pl], t[n4][4 * q + 3][pl]);
         }
     }
-    if (dbpart != nullptr) {
-        red[gl][ol] = sum;
+}
+
+// X NCHW -> XN[cls][g][iy][ix][c][4] (hi and lo): in padded coordinates (yp, xp) = (y + ph, x + pw), class
+// cls = (yp % sh) * sw + xp % sw, cell (iy, ix) = (yp / sh, xp / sw); the four values are images 4g..4g+3,
+// `Cp` channels per cell (zeros beyond C, outside the image and beyond N).  With `slab_hi` the same pass also
+// writes the forward kernel's class slabs S[cls * Q + c/4][n][iy][ix][4].
+// Block = 4 images x 32 channels x RY padded rows; it walks the rows' cells in chunks of 32 through shared
+// memory: reads coalesced along x, writes coalesced along the channels (XN) and along ix (slabs).
+__global__ void __launch_bounds__(256) pack_x_kernel(const float* __restrict__ x, float* __restrict__ xn_hi,
+                                                     float* __restrict__ xn_lo, float* __restrict__ slab_hi,
+                                                     float* __restrict__ slab_lo, int N, int C, int Cp, int H, int W, int Q,
+                                                     int ph, int pw, int Hc, int Wc, int N4, int RY, FastDiv dWp, FastDiv dsh,
+                                                     FastDiv dsw) {
+    __shared__ float t[4][32][33];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c0 = blockIdx.x * 32, g = blockIdx.z;
+    const int sh = (int)dsh.d, sw = (int)dsw.d;
+    const int Wp = Wc * sw, Hp = Hc * sh;
+    const int yp0 = blockIdx.y * RY;
+    const int rows = min(RY, Hp - yp0);
+    const int cells = rows * Wp;
+    for (int e0 = 0; e0 < cells; e0 += 32) {
+        {
+            const int e = e0 + lane;
+            uint32_t ry = 0, xp = 0;
+            if (e < cells) dWp.divmod((uint32_t)e, ry, xp);
+            const int y = yp0 + (int)ry - ph, xx = (int)xp - pw;
+            const bool in = e < cells && (unsigned)y < (unsigned)H && (unsigned)xx < (unsigned)W;
+            for (int q = warp; q < 128; q += 8) {
+                const int n4 = q >> 5, cl = q & 31;
+                const int n = 4 * g + n4, c = c0 + cl;
+                t[n4][cl][lane] = (in && n < N && c < C) ? __ldg(x + (((int64_t)n * C + c) * H + y) * W + xx) : 0.f;
+            }
+        }
         __syncthreads();
-        if (gl == 0 && o < K) dbpart[(int64_t)blockIdx.x * K + o] = (red[0][ol] + red[1][ol]) + (red[2][ol] + red[3][ol]);
+        if (xn_hi != nullptr) {
+            for (int i = threadIdx.x; i < 1024; i += 256) {
+                const int cl = i & 31, el = i >> 5;
+                const int e = e0 + el, c = c0 + cl;
+                if (e < cells && c < Cp) {
+                    uint32_t ry, xp, iy, cy, ix, cx;
+                    dWp.divmod((uint32_t)e, ry, xp);
+                    dsh.divmod((uint32_t)yp0 + ry, iy, cy);
+                    dsw.divmod(xp, ix, cx);
+                    const int cls = (int)cy * sw + (int)cx;
+                    store_split4(xn_hi, xn_lo, (((((int64_t)cls * N4 + g) * Hc + iy) * Wc + ix) * Cp + c) * 4, t[0][cl][el], t[1][cl][el],
+                                 t[2][cl][el], t[3][cl][el]);
+                }
+            }
+        }
+        if (slab_hi != nullptr) {
+            for (int i = threadIdx.x; i < 1024; i += 256) {
+                const int el = i & 31, rest = i >> 5;
+                const int n4 = rest >> 3, q = rest & 7;
+                const int e = e0 + el, n = 4 * g + n4, qq = (c0 >> 2) + q;
+                if (e < cells && n < N && qq < Q) {
+                    uint32_t ry, xp, iy, cy, ix, cx;
+                    dWp.divmod((uint32_t)e, ry, xp);
+                    dsh.divmod((uint32_t)yp0 + ry, iy, cy);
+                    dsw.divmod(xp, ix, cx);
+                    const int plane = ((int)cy * sw + (int)cx) * Q + qq;
+                    store_split4(slab_hi, slab_lo, ((((int64_t)plane * N + n) * Hc + iy) * Wc + ix) * 4, t[n4][4 * q][el],
+                                 t[n4][4 * q + 1][el], t[n4][4 * q + 2][el], t[n4][4 * q + 3][el]);
+                }
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -229,58 +309,6 @@ __global__ void __launch_bounds__(256) partial_rows_sum_kernel(const float* __re
     __syncthreads();
     if (bl == 0 && o < K)
         out[o] = ((red[0][ol] + red[1][ol]) + (red[2][ol] + red[3][ol])) + ((red[4][ol] + red[5][ol]) + (red[6][ol] + red[7][ol]));
-}
-
-// X NCHW -> chunk-major XC[(s*sh + cy)*N + n][y'][oxq][c][4] (hi and lo), Cp channels per chunk:
-// the four values X[n][c][y'*sh + cy][(4*oxq + j)*sw + s - pw], zero outside the image / beyond C.
-// One block per (n, group of RY image rows, block of 32 channels): the row segments are read coalesced into
-// shared memory and written out with the channel as the fastest index.
-__global__ void __launch_bounds__(256) split_x_chunk_major_kernel(const float* __restrict__ x, float* __restrict__ hi,
-                                                                  float* __restrict__ lo, int N, int C, int Cp, int H, int W,
-                                                                  int S, int sh, int sw, int pw, int Hc, int OWQ, int RY,
-                                                                  FastDiv dPerRow, FastDiv dOWQ, FastDiv dsh) {
-    extern __shared__ float row[];  // [RY][CB][W + 1]
-    const int CB = 32;  // channels per block (wider blocks measured slower)
-    const int cb = blockIdx.x, y0 = blockIdx.y * RY, n = blockIdx.z;  // y runs over Hc*sh rows (rows >= H are zeros)
-    const int c0 = cb * CB;
-    const int ws = W + 1;
-    const int ytot = Hc * sh;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // load: warp -> (row ry, channel cl), lanes along x
-    for (int q = warp; q < RY * CB; q += 8) {
-        const int ry = q / CB, cl = q - ry * CB;
-        const int c = c0 + cl, y = y0 + ry;
-        const bool in = c < C && y < H;
-        const float* src = x + (((int64_t)n * C + c) * H + y) * W;
-        for (int xx = lane; xx < W; xx += 32) row[q * ws + xx] = in ? __ldg(src + xx) : 0.f;
-    }
-    __syncthreads();
-    // store: CB/32 warps side by side cover the channels of one chunk, so a chunk is one contiguous run
-    const int cw = CB >> 5;
-    const int cl = lane + 32 * (warp % cw);
-    const int per_row = S * OWQ;
-    for (int i = warp / cw; i < RY * per_row; i += 8 / cw) {
-        uint32_t ry, rem, s, oxq, yq, cy;
-        dPerRow.divmod((uint32_t)i, ry, rem);
-        const int y = y0 + (int)ry;
-        if (y >= ytot) break;
-        dOWQ.divmod(rem, s, oxq);
-        dsh.divmod((uint32_t)y, yq, cy);
-        const float* rp = row + ((int)ry * CB + cl) * ws;
-        const int xb = 4 * (int)oxq * sw + (int)s - pw;
-        float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int xx = xb + j * sw;
-            v[j] = ((unsigned)xx < (unsigned)W) ? rp[xx] : 0.f;
-        }
-        uint4 h;
-        h.x = cvt_tf32_rna(v[0]); h.y = cvt_tf32_rna(v[1]); h.z = cvt_tf32_rna(v[2]); h.w = cvt_tf32_rna(v[3]);
-        const int64_t dst = (((((int64_t)((int)s * sh + (int)cy) * N + n) * Hc + yq) * OWQ + oxq) * Cp + c0 + cl) * 4;
-        *reinterpret_cast<uint4*>(hi + dst) = h;
-        *reinterpret_cast<float4*>(lo + dst) = make_float4(v[0] - __uint_as_float(h.x), v[1] - __uint_as_float(h.y),
-                                                           v[2] - __uint_as_float(h.z), v[3] - __uint_as_float(h.w));
-    }
 }
 
 template <typename T>
@@ -672,8 +700,13 @@ static void set_vec_store(TmaConvParams& prm) {
 // described by tensor maps; the caller then takes the cp.async path.
 // phase: which part of the call runs (FPROP_ALL, or one half for timing the two separately).
 enum : int { FPROP_ALL = 0, FPROP_PREPASS_ONLY = 1, FPROP_MAIN_ONLY = 2 };
+static int launch_pack_x(Context* c, const float* X, float* xn_hi, float* xn_lo, float* slab_hi, float* slab_lo,
+                         const ConvGeom& g, int Cp, int Q, int Hc, int Wc, cudaStream_t st);
+// xn_hi / xn_lo (optional): the same pass over X also leaves the filter-gradient kernel's packed input
+// (xn_cp channels per cell) there, for a backward pass that follows.
 static int conv_fprop_tma(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
-                          int act, void* ws, cudaStream_t st, bool* used, int phase = FPROP_ALL) {
+                          int act, void* ws, cudaStream_t st, bool* used, int phase = FPROP_ALL, float* xn_hi = nullptr,
+                          float* xn_lo = nullptr, int xn_cp = 0) {
     *used = false;
     if (!tma_stride_ok(g) || tensor_map_encoder() == nullptr) return FXB_OK;
     const TmaFpropLayout l = tma_fprop_layout(g);
@@ -686,12 +719,17 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     if (!encode_filter_maps(prm, w.b_hi, w.b_lo, l.rows_pad, g.RS * l.Q, bn)) return FXB_OK;
     *used = true;
     if (phase != FPROP_MAIN_ONLY) {
-        const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
-        const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
-        split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
-                                                                  total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
-                                                                  FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
-        int rc = launch_status(c, "split_image_to_class_slabs_kernel");
+        int rc;
+        if (xn_hi != nullptr) {
+            rc = launch_pack_x(c, X, xn_hi, xn_lo, w.a_hi, w.a_lo, g, xn_cp, l.Q, l.Hc, l.Wc, st);
+        } else {
+            const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
+            const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
+            split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
+                                                                      total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
+                                                                      FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
+            rc = launch_status(c, "split_image_to_class_slabs_kernel");
+        }
         if (rc) return rc;
         FilterClassBase fc{};
         const int ftotal = g.RS * l.Q * l.rows_pad;
@@ -807,7 +845,7 @@ static bool dgrad_class(const ConvGeom& g, int cy, int cx, DgradClass& cl) {
 // and grouped by stride-residue class, one launch per class.  *used = false when some class cannot be
 // described by tensor maps (nothing has been launched then).
 static int conv_dgrad_tma(Context* c, const float* dY, const float* Yact, const float* W, float* dX, const ConvGeom& g,
-                          int act, void* ws, cudaStream_t st, bool* used) {
+                          int act, void* ws, cudaStream_t st, bool* used, bool slabs_ready = false) {
     *used = false;
     if (!tma_stride_ok(g) || tensor_map_encoder() == nullptr) return FXB_OK;
     const int K4 = (g.K + 3) / 4;
@@ -849,8 +887,11 @@ static int conv_dgrad_tma(Context* c, const float* dY, const float* Yact, const 
             live[ci] = true;
         }
     *used = true;
-    int rc = launch_split_image(c, dY, act == FXB_ACT_NONE ? nullptr : Yact, w.a_hi, w.a_lo, g.N, g.K, g.P, act, st, true);
-    if (rc) return rc;
+    int rc = FXB_OK;
+    if (!slabs_ready) {  // (the fused backward's operand pass has written the dZ slabs already)
+        rc = launch_split_image(c, dY, act == FXB_ACT_NONE ? nullptr : Yact, w.a_hi, w.a_lo, g.N, g.K, g.P, act, st, true);
+        if (rc) return rc;
+    }
     const int ftotal = g.RS * K4 * rows_pad;
     const int fblocks = std::max(1, std::min((ftotal + 255) / 256, c->sm_count * 8));
     split_filter_chunk_major_kernel<<<fblocks, 256, 0, st>>>(W, w.b_hi, w.b_lo, g.K, g.C, g.R, g.S, K4, g.C, rows_pad, 1, g.sh, g.sw, fc);
@@ -998,20 +1039,19 @@ __global__ void __launch_bounds__(256) smallc_db_finish_kernel(const T* __restri
 }
 
 // ---- tensor-map filter-gradient path ---------------------------------------------------------
+// Geometry and workspace plan.  Workspace order: [DZN hi | DZN lo | XN hi | XN lo | split-K partials | db partials];
+// the XN pair is left out when the caller brings its own (prepared by the forward pass).
 struct TmaWgradLayout {
     bool ok;
-    int Kp, Cp, Cb, tpt, cblocks, PQ, OWQ, Hc, ips, tm, tn, splits, stages_total, stages_per_split, dz_blocks;
-    int64_t dz_floats, xc_floats, part_floats, dbpart_floats;
-    size_t bytes;
+    int Kp, Cp, Cb, tpt, cblocks, n4, ncls, Hc, Wc, bw, bh, PWs, PHs, spg, tm, tn, splits, stages_total, stages_per_split;
+    int pblocks, db_rows;
+    int64_t dz_floats, xn_floats, part_floats, dbpart_floats;
+    size_t bytes, bytes_without_xn;
 };
 static TmaWgradLayout tma_wgrad_layout(const Context* c, const ConvGeom& g) {
     TmaWgradLayout l{};
     l.ok = false;
-    if (g.OW % 4 != 0 || g.sh > 8 || g.S > 32 || g.W > 256 || g.N > 65535) return l;
-    l.OWQ = g.OW / 4;
-    l.PQ = g.P / 4;
-    if (!(l.PQ % TMA_KCH == 0 || (TMA_KCH % l.PQ == 0 && g.N % (TMA_KCH / l.PQ) == 0))) return l;
-    l.ips = l.PQ >= TMA_KCH ? 1 : TMA_KCH / l.PQ;
+    if (!tma_stride_ok(g) || g.S > 32 || g.R > 32) return l;
     l.Cp = round_up(g.C, 16);
     if (l.Cp > 128) l.Cp = round_up(g.C, 128);
     else if (l.Cp > 64) l.Cp = 128;
@@ -1024,104 +1064,110 @@ static TmaWgradLayout tma_wgrad_layout(const Context* c, const ConvGeom& g) {
     l.tpt = 128 / l.Cb;
     l.cblocks = std::max(1, l.Cp / 128);
     l.Kp = round_up(g.K, 16);
-    l.Hc = (g.H + g.sh - 1) / g.sh;
-    const int64_t G = (int64_t)g.N * l.PQ;
-    if (G >= ((int64_t)1 << 31) / 16) return l;
-    l.stages_total = (int)((G + TMA_KCH - 1) / TMA_KCH);
+    l.n4 = (g.N + 3) / 4;
+    l.ncls = g.sh * g.sw;
+    l.Hc = (g.H - 1 + g.ph) / g.sh + 1;
+    l.Wc = (g.W - 1 + g.pw) / g.sw + 1;
+    l.bw = std::min(TMA_KCH, 1 << log2_ceil(g.OW));
+    l.bh = TMA_KCH / l.bw;
+    l.PWs = (g.OW + l.bw - 1) / l.bw;
+    l.PHs = (g.OH + l.bh - 1) / l.bh;
+    l.spg = l.PWs * l.PHs;
+    const int64_t stages = (int64_t)l.n4 * l.spg;
+    if (stages >= ((int64_t)1 << 30) || (int64_t)l.ncls * l.n4 >= ((int64_t)1 << 30)) return l;
+    l.stages_total = (int)stages;
     l.tm = (g.K + 127) / 128;
     l.tn = l.cblocks > 1 ? g.RS * l.cblocks : (g.RS + l.tpt - 1) / l.tpt;
     const int tiles = l.tm * l.tn;
     int splits = std::max(1, std::min(l.stages_total / 8, c->sm_count / tiles));  // one wave of CTAs
     l.stages_per_split = (l.stages_total + splits - 1) / splits;
     l.splits = (l.stages_total + l.stages_per_split - 1) / l.stages_per_split;
-    l.dz_blocks = (int)((G + DZ_GB - 1) / DZ_GB);
-    l.dz_floats = G * l.Kp * 4;
-    l.xc_floats = (int64_t)g.S * g.sh * g.N * l.Hc * l.OWQ * l.Cp * 4;
+    l.pblocks = (g.P + 31) / 32;
+    l.db_rows = l.n4 * l.pblocks;
+    l.dz_floats = (int64_t)l.n4 * g.P * l.Kp * 4;
+    l.xn_floats = (int64_t)l.ncls * l.n4 * l.Hc * l.Wc * l.Cp * 4;
+    if (l.dz_floats >= ((int64_t)1 << 33) || l.xn_floats >= ((int64_t)1 << 33)) return l;
     l.part_floats = l.splits > 1 ? (int64_t)l.splits * g.K * g.CRS : 0;
-    l.dbpart_floats = (int64_t)l.dz_blocks * g.K;
-    l.bytes = 2 * align_up256((size_t)l.dz_floats * 4) + 2 * align_up256((size_t)l.xc_floats * 4) +
-              align_up256((size_t)l.part_floats * 4) + align_up256((size_t)l.dbpart_floats * 4);
+    l.dbpart_floats = (int64_t)l.db_rows * g.K;
+    l.bytes_without_xn = 2 * align_up256((size_t)l.dz_floats * 4) + align_up256((size_t)l.part_floats * 4) +
+                         align_up256((size_t)l.dbpart_floats * 4);
+    l.bytes = l.bytes_without_xn + 2 * align_up256((size_t)l.xn_floats * 4);
     l.ok = true;
     return l;
 }
 
-static int conv_wgrad_tma(Context* c, const float* X, const float* dY, const float* Yact, float* dW, float* db,
-                          const ConvGeom& g, int act, void* ws, size_t ws_bytes, cudaStream_t st, bool* used) {
-    *used = false;
-    if (tensor_map_encoder() == nullptr) return FXB_OK;
-    const TmaWgradLayout l = tma_wgrad_layout(c, g);
-    if (!l.ok || ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255) != 0 || ws_bytes < l.bytes) return FXB_OK;
-    if ((reinterpret_cast<uintptr_t>(dY) & 15) != 0 || (Yact != nullptr && (reinterpret_cast<uintptr_t>(Yact) & 15) != 0))
-        return FXB_OK;
-    char* p = static_cast<char*>(ws);
-    float* dz_hi = reinterpret_cast<float*>(p); p += align_up256((size_t)l.dz_floats * 4);
-    float* dz_lo = reinterpret_cast<float*>(p); p += align_up256((size_t)l.dz_floats * 4);
-    float* xc_hi = reinterpret_cast<float*>(p); p += align_up256((size_t)l.xc_floats * 4);
-    float* xc_lo = reinterpret_cast<float*>(p); p += align_up256((size_t)l.xc_floats * 4);
-    float* part = reinterpret_cast<float*>(p); p += align_up256((size_t)l.part_floats * 4);
-    float* dbpart = reinterpret_cast<float*>(p);
-    const int64_t G = (int64_t)g.N * l.PQ;
+// x -> XN (and, with slab pointers, the forward kernel's class slabs) in one pass.
+static int launch_pack_x(Context* c, const float* X, float* xn_hi, float* xn_lo, float* slab_hi, float* slab_lo,
+                         const ConvGeom& g, int Cp, int Q, int Hc, int Wc, cudaStream_t st) {
+    const int n4 = (g.N + 3) / 4;
+    const int Wp = Wc * g.sw, Hp = Hc * g.sh;
+    const int chans = std::max(xn_hi ? Cp : 0, slab_hi ? Q * 4 : 0);
+    const int ry = std::max(1, std::min(Hp, (256 + Wp - 1) / Wp));  // about eight 32-cell chunks per block
+    if (n4 > 65535 || (Hp + ry - 1) / ry > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Conv2D batch too large for the packed operand pass");
+    dim3 grid((chans + 31) / 32, (Hp + ry - 1) / ry, n4);
+    pack_x_kernel<<<grid, 256, 0, st>>>(X, xn_hi, xn_lo, slab_hi, slab_lo, g.N, g.C, Cp, g.H, g.W, Q, g.ph, g.pw, Hc, Wc, n4, ry,
+                                        FastDiv((uint32_t)Wp), FastDiv((uint32_t)g.sh), FastDiv((uint32_t)g.sw));
+    return launch_status(c, "pack_x_kernel");
+}
+// dY (* act'(Y)) -> DZN (+ channel slabs for the input gradient) (+ bias gradient).
+static int launch_pack_dz(Context* c, const float* dY, const float* Yact, float* dzn_hi, float* dzn_lo, float* slab_hi,
+                          float* slab_lo, float* dbpart, float* db, const ConvGeom& g, const TmaWgradLayout& l, int act,
+                          cudaStream_t st) {
+    if (l.n4 > 65535 || (l.Kp + 31) / 32 > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Conv2D batch too large for the packed operand pass");
+    dim3 grid(l.pblocks, (l.Kp + 31) / 32, l.n4);
+    pack_dz_kernel<<<grid, 256, 0, st>>>(dY, act == FXB_ACT_NONE ? nullptr : Yact, dzn_hi, dzn_lo, slab_hi, slab_lo,
+                                         db ? dbpart : nullptr, g.N, g.K, l.Kp, g.P, act, c->sigmoid_grad_math);
+    int rc = launch_status(c, "pack_dz_kernel");
+    if (rc) return rc;
+    if (db) {
+        partial_rows_sum_kernel<<<(g.K + 31) / 32, 256, 0, st>>>(dbpart, db, g.K, l.db_rows);
+        rc = launch_status(c, "partial_rows_sum_kernel");
+    }
+    return rc;
+}
 
+// The contraction itself, from prepared operands.  Returns false in *used (nothing launched) when a
+// tensor map cannot be encoded.
+static int launch_wgrad_tma(Context* c, const float* dz_hi, const float* dz_lo, const float* xn_hi, const float* xn_lo,
+                            float* part, float* dW, const ConvGeom& g, const TmaWgradLayout& l, cudaStream_t st, bool* used) {
+    *used = false;
     TmaWgradParams prm;
     {
-        const uint64_t dims[3] = {64, (uint64_t)l.Kp / 16, (uint64_t)G};
-        const uint64_t str[2] = {256, (uint64_t)l.Kp * 16};
-        const uint32_t box[3] = {64, 8, (uint32_t)TMA_KCH};
-        if (!encode_f32_map(&prm.a_hi, dz_hi, 3, dims, str, box) || !encode_f32_map(&prm.a_lo, dz_lo, 3, dims, str, box))
+        const uint64_t dims[5] = {64, (uint64_t)l.Kp / 16, (uint64_t)g.OW, (uint64_t)g.OH, (uint64_t)l.n4};
+        const uint64_t str[4] = {256, (uint64_t)l.Kp * 16, (uint64_t)g.OW * l.Kp * 16, (uint64_t)g.P * l.Kp * 16};
+        const uint32_t box[5] = {64, 8, (uint32_t)l.bw, (uint32_t)l.bh, 1};
+        if (!encode_f32_map(&prm.a_hi, dz_hi, 5, dims, str, box) || !encode_f32_map(&prm.a_lo, dz_lo, 5, dims, str, box))
             return FXB_OK;
     }
     {
-        const uint64_t chunks_img = (uint64_t)l.Hc * l.OWQ;
-        const uint64_t dims[4] = {64, (uint64_t)l.Cp / 16, chunks_img, (uint64_t)g.S * g.sh * g.N};
-        const uint64_t str[3] = {256, (uint64_t)l.Cp * 16, chunks_img * l.Cp * 16};
-        const uint32_t box[4] = {64, (uint32_t)l.Cb / 16, (uint32_t)std::min(TMA_KCH, l.PQ), (uint32_t)l.ips};
-        if (!encode_f32_map(&prm.b_hi, xc_hi, 4, dims, str, box) || !encode_f32_map(&prm.b_lo, xc_lo, 4, dims, str, box))
+        const uint64_t dims[5] = {64, (uint64_t)l.Cp / 16, (uint64_t)l.Wc, (uint64_t)l.Hc, (uint64_t)l.ncls * l.n4};
+        const uint64_t str[4] = {256, (uint64_t)l.Cp * 16, (uint64_t)l.Wc * l.Cp * 16, (uint64_t)l.Hc * l.Wc * l.Cp * 16};
+        const uint32_t box[5] = {64, (uint32_t)l.Cb / 16, (uint32_t)l.bw, (uint32_t)l.bh, 1};
+        if (!encode_f32_map(&prm.b_hi, xn_hi, 5, dims, str, box) || !encode_f32_map(&prm.b_lo, xn_lo, 5, dims, str, box))
             return FXB_OK;
     }
     *used = true;
-    {
-        dim3 grid(l.dz_blocks, (l.Kp + 63) / 64);
-        split_dz_chunk_major_kernel<<<grid, 256, 0, st>>>(dY, act == FXB_ACT_NONE ? nullptr : Yact, dz_hi, dz_lo,
-                                                         db ? dbpart : nullptr, g.K, l.Kp, l.PQ, G, act, c->sigmoid_grad_math);
-        int rc = launch_status(c, "split_dz_chunk_major_kernel");
-        if (rc) return rc;
-        if (db) {
-            partial_rows_sum_kernel<<<(g.K + 31) / 32, 256, 0, st>>>(dbpart, db, g.K, l.dz_blocks);
-            rc = launch_status(c, "partial_rows_sum_kernel");
-            if (rc) return rc;
-        }
-        const int cbw = 32;
-        const int ry = std::max(1, std::min(8, 10240 / (cbw * (g.W + 1))));
-        dim3 xgrid(l.Cp / cbw, (l.Hc * g.sh + ry - 1) / ry, g.N);
-        split_x_chunk_major_kernel<<<xgrid, 256, (size_t)ry * cbw * (g.W + 1) * 4, st>>>(X, xc_hi, xc_lo, g.N, g.C, l.Cp, g.H, g.W,
-                                                                                       g.S, g.sh, g.sw, g.pw, l.Hc, l.OWQ, ry,
-                                                                                       FastDiv((uint32_t)(g.S * l.OWQ)),
-                                                                                       FastDiv((uint32_t)l.OWQ), FastDiv((uint32_t)g.sh));
-        rc = launch_status(c, "split_x_chunk_major_kernel");
-        if (rc) return rc;
-    }
     prm.tm = l.tm; prm.tn = l.tn; prm.splits = l.splits;
     prm.stages_total = l.stages_total; prm.stages_per_split = l.stages_per_split;
     prm.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
     prm.K = g.K; prm.C = g.C; prm.RS = g.RS; prm.S = g.S;
     prm.Cb = l.Cb; prm.tpt = l.tpt; prm.cblocks = l.cblocks;
-    prm.sh = g.sh; prm.ph = g.ph; prm.PQ = l.PQ; prm.OWQ = l.OWQ; prm.N = g.N; prm.imgs_per_stage = l.ips;
+    prm.sh = g.sh; prm.sw = g.sw; prm.n4 = l.n4; prm.ncls = l.ncls; prm.bw = l.bw; prm.bh = l.bh;
+    prm.dSpg.init((uint32_t)l.spg); prm.dPW.init((uint32_t)l.PWs);
     prm.out = l.splits > 1 ? part : dW;
     prm.split_stride = (int64_t)g.K * g.CRS;
-    {
-        using Cfg = TmaCfg<128>;
-        auto kern = umma_tma_wgrad_kernel<128>;
-        static bool attr_set[64] = {};
-        if (!attr_set[c->device & 63]) {
-            FXB_CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-            attr_set[c->device & 63] = true;
-        }
-        const long long items = (long long)l.tm * l.tn * l.splits;
-        const int grid = (int)std::min<long long>(items, c->sm_count);
-        kern<<<grid, TMA_THREADS, Cfg::SMEM_BYTES, st>>>(prm, c->d_status);
-        int rc = launch_status(c, "umma_tma_wgrad_kernel");
-        if (rc) return rc;
+    using Cfg = TmaCfg<128>;
+    auto kern = umma_tma_wgrad_kernel<128>;
+    static bool attr_set[64] = {};
+    if (!attr_set[c->device & 63]) {
+        FXB_CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set[c->device & 63] = true;
     }
+    const long long items = (long long)l.tm * l.tn * l.splits;
+    const int grid = (int)std::min<long long>(items, c->sm_count);
+    kern<<<grid, TMA_THREADS, Cfg::SMEM_BYTES, st>>>(prm, c->d_status);
+    int rc = launch_status(c, "umma_tma_wgrad_kernel");
+    if (rc) return rc;
     if (l.splits > 1) {
         const int64_t n = (int64_t)g.K * g.CRS;
         const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)c->sm_count * 8);
@@ -1129,6 +1175,58 @@ static int conv_wgrad_tma(Context* c, const float* X, const float* dY, const flo
         return launch_status(c, "splitk_reduce");
     }
     return FXB_OK;
+}
+
+struct WgradWs { float *dz_hi, *dz_lo, *xn_hi, *xn_lo, *part, *dbpart; };
+static WgradWs carve_wgrad_ws(void* ws, const TmaWgradLayout& l, bool with_xn) {
+    WgradWs w{};
+    char* p = static_cast<char*>(ws);
+    w.dz_hi = reinterpret_cast<float*>(p); p += align_up256((size_t)l.dz_floats * 4);
+    w.dz_lo = reinterpret_cast<float*>(p); p += align_up256((size_t)l.dz_floats * 4);
+    if (with_xn) {
+        w.xn_hi = reinterpret_cast<float*>(p); p += align_up256((size_t)l.xn_floats * 4);
+        w.xn_lo = reinterpret_cast<float*>(p); p += align_up256((size_t)l.xn_floats * 4);
+    }
+    w.part = reinterpret_cast<float*>(p); p += align_up256((size_t)l.part_floats * 4);
+    w.dbpart = reinterpret_cast<float*>(p);
+    return w;
+}
+
+// xn_hi / xn_lo: the packed input prepared earlier (by the forward pass), or nullptr: packed here.
+static int conv_wgrad_tma(Context* c, const float* X, const float* dY, const float* Yact, float* dW, float* db,
+                          const ConvGeom& g, int act, void* ws, size_t ws_bytes, cudaStream_t st, bool* used,
+                          const float* xn_hi = nullptr, const float* xn_lo = nullptr) {
+    *used = false;
+    if (tensor_map_encoder() == nullptr) return FXB_OK;
+    const TmaWgradLayout l = tma_wgrad_layout(c, g);
+    const bool own_xn = xn_hi == nullptr;
+    if (!l.ok || ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255) != 0 || ws_bytes < (own_xn ? l.bytes : l.bytes_without_xn))
+        return FXB_OK;
+    const WgradWs w = carve_wgrad_ws(ws, l, own_xn);
+    if (own_xn) { xn_hi = w.xn_hi; xn_lo = w.xn_lo; }
+    // probe the tensor maps before anything is launched (the caller falls back to the gather path otherwise)
+    {
+        TmaWgradParams probe;
+        const uint64_t dims[5] = {64, (uint64_t)l.Kp / 16, (uint64_t)g.OW, (uint64_t)g.OH, (uint64_t)l.n4};
+        const uint64_t str[4] = {256, (uint64_t)l.Kp * 16, (uint64_t)g.OW * l.Kp * 16, (uint64_t)g.P * l.Kp * 16};
+        const uint32_t box[5] = {64, 8, (uint32_t)l.bw, (uint32_t)l.bh, 1};
+        const uint64_t dimsb[5] = {64, (uint64_t)l.Cp / 16, (uint64_t)l.Wc, (uint64_t)l.Hc, (uint64_t)l.ncls * l.n4};
+        const uint64_t strb[4] = {256, (uint64_t)l.Cp * 16, (uint64_t)l.Wc * l.Cp * 16, (uint64_t)l.Hc * l.Wc * l.Cp * 16};
+        const uint32_t boxb[5] = {64, (uint32_t)l.Cb / 16, (uint32_t)l.bw, (uint32_t)l.bh, 1};
+        if (!encode_f32_map(&probe.a_hi, w.dz_hi, 5, dims, str, box) || !encode_f32_map(&probe.b_hi, xn_hi, 5, dimsb, strb, boxb))
+            return FXB_OK;
+    }
+    *used = true;
+    int rc = launch_pack_dz(c, dY, Yact, w.dz_hi, w.dz_lo, nullptr, nullptr, w.dbpart, db, g, l, act, st);
+    if (rc) return rc;
+    if (own_xn) {
+        rc = launch_pack_x(c, X, w.xn_hi, w.xn_lo, nullptr, nullptr, g, l.Cp, 0, l.Hc, l.Wc, st);
+        if (rc) return rc;
+    }
+    bool launched = false;
+    rc = launch_wgrad_tma(c, w.dz_hi, w.dz_lo, xn_hi, xn_lo, w.part, dW, g, l, st, &launched);
+    if (rc == FXB_OK && !launched) return fail(c, FXB_ERR_CUDA, "filter gradient: tensor map encoding failed after the probe");
+    return rc;
 }
 
 template <typename T>
@@ -1178,6 +1276,96 @@ static int conv_wgrad_impl(Context* c, const T* X, const T* dY, const T* Yact, T
     // dW[ko][crs]: row m = crs inside one "image" of plane CRS, column n = ko with stride CRS.
     auto ow = make_plane_writer<T>(dW, g.CRS, (int64_t)g.K * g.CRS, nullptr, FXB_ACT_NONE, p.M, p.N);
     return launch_contract(c, la, lb, ow, p, st);
+}
+
+// ---- whole backward of a conv layer (dW, db, dX) with one operand pass over dY ----------------------
+// Packed input of the filter-gradient kernel: [XN hi | XN lo].  0 when the layer does not take the
+// tensor-map filter-gradient path.
+static size_t conv_packed_bytes(const Context* c, const ConvGeom& g) {
+    if (g.CRS <= SMALLC_K || tensor_map_encoder() == nullptr) return 0;
+    const TmaWgradLayout l = tma_wgrad_layout(c, g);
+    return l.ok ? 2 * align_up256((size_t)l.xn_floats * 4) : 0;
+}
+static size_t conv_backward_bytes(const Context* c, const ConvGeom& g) {
+    const TmaWgradLayout l = tma_wgrad_layout(c, g);
+    return l.ok ? align_up256(dgrad_split_bytes(g)) + l.bytes : 0;
+}
+
+// Forward pass that also leaves the packed input for the backward pass in `packed` (same values as the
+// plain forward).  *packed_written reports whether it did (only the tensor-map path can).
+static int conv_fprop_packing(Context* c, const float* X, const float* W, const float* bias, float* Y,
+                              const fxb_conv2d_desc* d, int act, void* ws, size_t ws_bytes, void* packed, size_t packed_bytes,
+                              int* packed_written, cudaStream_t st) {
+    if (packed_written) *packed_written = 0;
+    ConvGeom g;
+    int rc = make_geom(c, d, g);
+    if (rc) return rc;
+    const size_t need = conv_packed_bytes(c, g);
+    if (packed != nullptr && need > 0 && packed_bytes >= need && (reinterpret_cast<uintptr_t>(packed) & 255) == 0 && X && W && Y &&
+        act >= FXB_ACT_NONE && act <= FXB_ACT_TANH && c->operand_path == FXB_PATH_AUTO && ws != nullptr &&
+        (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes >= fprop_split_bytes(g)) {
+        const TmaWgradLayout l = tma_wgrad_layout(c, g);
+        float* xn_hi = static_cast<float*>(packed);
+        float* xn_lo = reinterpret_cast<float*>(static_cast<char*>(packed) + align_up256((size_t)l.xn_floats * 4));
+        bool used = false;
+        rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, FPROP_ALL, xn_hi, xn_lo, l.Cp);
+        if (rc) return rc;
+        if (used) {
+            if (packed_written) *packed_written = 1;
+            return FXB_OK;
+        }
+    }
+    return conv_fprop_impl<float>(c, X, W, bias, Y, d, act, ws, ws_bytes, st);
+}
+
+template <typename T>
+static int conv_backward_impl(Context* c, const T* X, const T* dY, const T* Yact, const T* W, T* dX, T* dW, T* db,
+                              const fxb_conv2d_desc* d, int act, void* ws, size_t ws_bytes, const void* packed,
+                              cudaStream_t st) {
+    ConvGeom g;
+    int rc = make_geom(c, d, g);
+    if (rc) return rc;
+    FXB_CHECK_ARG(c, X && dY && W && dW, "Conv2d backward got a null buffer");
+    FXB_CHECK_ARG(c, act == FXB_ACT_NONE || Yact != nullptr, "Fused activation backward needs the layer output");
+    if constexpr (sizeof(T) == 4) {
+        const TmaWgradLayout l = tma_wgrad_layout(c, g);
+        const bool fused = c->operand_path == FXB_PATH_AUTO && dX != nullptr && g.CRS > SMALLC_K && l.ok && tensor_map_encoder() != nullptr &&
+                           ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes >= conv_backward_bytes(c, g);
+        if (fused) {
+            // region 1: the input-gradient operands (dZ slabs, filter); region 2: the filter-gradient operands
+            const size_t r1 = align_up256(dgrad_split_bytes(g));
+            void* ws2 = static_cast<char*>(ws) + r1;
+            const int K4 = (g.K + 3) / 4;
+            const int bn = tile_cols(g.C);
+            const SplitWs sw = carve_split_ws(ws, (int64_t)g.N * K4 * g.P * 4, (int64_t)round_up(g.C, bn) * g.RS * K4 * 4);
+            const float* xn_hi = static_cast<const float*>(packed);
+            const float* xn_lo = packed ? reinterpret_cast<const float*>(static_cast<const char*>(packed) + align_up256((size_t)l.xn_floats * 4))
+                                        : nullptr;
+            const bool own_xn = packed == nullptr;
+            const WgradWs w = carve_wgrad_ws(ws2, l, own_xn);
+            if (own_xn) { xn_hi = w.xn_hi; xn_lo = w.xn_lo; }
+            rc = launch_pack_dz(c, dY, Yact, w.dz_hi, w.dz_lo, sw.a_hi, sw.a_lo, w.dbpart, db, g, l, act, st);
+            if (rc) return rc;
+            if (own_xn) {
+                rc = launch_pack_x(c, X, w.xn_hi, w.xn_lo, nullptr, nullptr, g, l.Cp, 0, l.Hc, l.Wc, st);
+                if (rc) return rc;
+            }
+            bool launched = false;
+            rc = launch_wgrad_tma(c, w.dz_hi, w.dz_lo, xn_hi, xn_lo, w.part, dW, g, l, st, &launched);
+            if (rc) return rc;
+            if (!launched) {  // no tensor map for this shape: the general filter-gradient path (region 2 is free again)
+                rc = conv_wgrad_impl<float>(c, X, dY, Yact, dW, nullptr, d, act, ws2, ws_bytes - r1, st);
+                if (rc) return rc;
+            }
+            bool used = false;
+            rc = conv_dgrad_tma(c, dY, Yact, W, dX, g, act, ws, st, &used, true);
+            if (rc || used) return rc;
+            return conv_dgrad_impl<float>(c, dY, Yact, W, dX, d, act, ws, ws_bytes, st);
+        }
+    }
+    rc = conv_wgrad_impl<T>(c, X, dY, Yact, dW, db, d, act, ws, ws_bytes, st);
+    if (rc || dX == nullptr) return rc;
+    return conv_dgrad_impl<T>(c, dY, Yact, W, dX, d, act, ws, ws_bytes, st);
 }
 
 template <typename T>
@@ -1313,6 +1501,40 @@ using namespace fxb;
 
 FXB_CONTRACT_API(f32, float)
 FXB_CONTRACT_API(f64, double)
+
+extern "C" int fxb_conv2d_backward_f32(fxb_handle_t h, const float* X, const float* dY, const float* Y, const float* W, float* dX,
+                                       float* dW, float* db, const fxb_conv2d_desc* d, int act, void* ws, size_t wsb,
+                                       const void* packed_input, fxb_stream_t s) {
+    NEED_HANDLE(h);
+    return conv_backward_impl<float>(CTX(h), X, dY, Y, W, dX, dW, db, d, act, ws, wsb, packed_input, ST(s));
+}
+extern "C" int fxb_conv2d_backward_f64(fxb_handle_t h, const double* X, const double* dY, const double* Y, const double* W,
+                                       double* dX, double* dW, double* db, const fxb_conv2d_desc* d, int act, void* ws,
+                                       size_t wsb, const void* packed_input, fxb_stream_t s) {
+    NEED_HANDLE(h);
+    (void)packed_input;  // f64 has no packed operands
+    return conv_backward_impl<double>(CTX(h), X, dY, Y, W, dX, dW, db, d, act, ws, wsb, nullptr, ST(s));
+}
+extern "C" int fxb_conv2d_bias_act_fwd_packing_f32(fxb_handle_t h, const float* X, const float* W, const float* bias, float* Y,
+                                                   const fxb_conv2d_desc* d, int act, void* ws, size_t wsb, void* packed_input,
+                                                   size_t packed_bytes, int* packed_written, fxb_stream_t s) {
+    NEED_HANDLE(h);
+    return conv_fprop_packing(CTX(h), X, W, bias, Y, d, act, ws, wsb, packed_input, packed_bytes, packed_written, ST(s));
+}
+extern "C" size_t fxb_conv2d_packed_input_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
+    if (!h || !d || elem != 4) return 0;
+    ConvGeom g;
+    if (make_geom(CTX(h), d, g) != FXB_OK) return 0;
+    return conv_packed_bytes(CTX(h), g);
+}
+extern "C" size_t fxb_conv2d_backward_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
+    if (!h || !d) return 0;
+    ConvGeom g;
+    if (make_geom(CTX(h), d, g) != FXB_OK) return 0;
+    size_t need = std::max(fxb_conv2d_wgrad_workspace_bytes(h, d, elem), fxb_conv2d_dgrad_workspace_bytes(h, d, elem));
+    if (elem == 4) need = std::max(need, conv_backward_bytes(CTX(h), g));
+    return need;
+}
 
 extern "C" size_t fxb_gemm_workspace_bytes(fxb_handle_t h, int64_t M, int64_t N, int64_t K, size_t elem) {
     if (!h || M <= 0 || N <= 0 || K <= 0) return 0;

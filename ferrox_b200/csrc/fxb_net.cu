@@ -15,6 +15,10 @@ struct NetLayer {
     int64_t k, stride, pad;
     int64_t w_off = -1, b_off = -1, end_off = -1;  // elements in the flat parameter buffer
     int64_t act_off = 0;                           // bytes in the arena: this layer's output
+    // conv layers (f32): the layer input packed for the filter-gradient kernel, written by the forward
+    // pass and read by the backward pass of the same step
+    size_t packed_off = 0, packed_bytes = 0;
+    int packed_valid = 0;
     int param_index = -1;
     fxb_conv2d_desc cd{};
 };
@@ -48,6 +52,8 @@ extern "C" size_t fxb_linear_bwd_workspace_bytes(fxb_handle_t, int64_t, int64_t,
 extern "C" size_t fxb_conv2d_wgrad_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_dgrad_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
+extern "C" size_t fxb_conv2d_backward_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
+extern "C" size_t fxb_conv2d_packed_input_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 
 extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_desc* layers, int nlayers, int64_t batch,
                               int64_t in_c, int64_t in_h, int64_t in_w, fxb_net_t* out) {
@@ -78,7 +84,10 @@ extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_
             L.w_off = n->nparams; L.b_off = L.w_off + L.out_c * cc * L.k * L.k; L.end_off = L.b_off + L.out_c;
             ws = std::max(ws, fxb_conv2d_wgrad_workspace_bytes(h, &L.cd, elem_size));
             ws = std::max(ws, fxb_conv2d_fprop_workspace_bytes(h, &L.cd, elem_size));
-            if (i > 0) ws = std::max(ws, fxb_conv2d_dgrad_workspace_bytes(h, &L.cd, elem_size));
+            if (i > 0) {
+                ws = std::max(ws, fxb_conv2d_backward_workspace_bytes(h, &L.cd, elem_size));
+                L.packed_bytes = fxb_conv2d_packed_input_bytes(h, &L.cd, elem_size);
+            }
         } else if (L.kind == FXB_LAYER_LINEAR) {
             if (hh != 1 || ww != 1 || layers[i].out_channels <= 0) {
                 delete n;
@@ -101,6 +110,10 @@ extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_
             const size_t elems = (size_t)batch * L.out_c * L.out_h * L.out_w;
             off += align256(elems * elem_size);
             max_act = std::max(max_act, elems);
+            if (L.packed_bytes) {
+                L.packed_off = off;
+                off += align256(L.packed_bytes);
+            }
         }
         cc = L.out_c; hh = L.out_h; ww = L.out_w;
         n->layers.push_back(L);
@@ -151,21 +164,26 @@ extern "C" int fxb_net_bind(fxb_net_t net, void* params, void* grads, void* aren
 namespace {
 template <typename T> struct Api;
 template <> struct Api<float> {
-    static constexpr auto conv_fwd = fxb_conv2d_bias_act_fwd_f32;
+    static int conv_fwd(fxb_handle_t h, const float* x, const float* w, const float* b, float* y, const fxb_conv2d_desc* d, int act,
+                        void* ws, size_t wsb, void* packed, size_t packed_bytes, int* written, fxb_stream_t st) {
+        return fxb_conv2d_bias_act_fwd_packing_f32(h, x, w, b, y, d, act, ws, wsb, packed, packed_bytes, written, st);
+    }
     static constexpr auto lin_fwd = fxb_linear_fwd_f32;
     static constexpr auto lin_bwd = fxb_linear_bwd_f32;
-    static constexpr auto dgrad = fxb_conv2d_dgrad_act_f32;
-    static constexpr auto wgrad = fxb_conv2d_wgrad_bias_act_f32;
+    static constexpr auto conv_bwd = fxb_conv2d_backward_f32;
     static int ce(fxb_handle_t h, const void* z, const void* t, void* l, void* g, int64_t B, int64_t C, double s, fxb_stream_t st) {
         return fxb_softmax_ce_f32(h, (const float*)z, (const float*)t, (float*)l, (float*)g, B, C, (float)s, st);
     }
 };
 template <> struct Api<double> {
-    static constexpr auto conv_fwd = fxb_conv2d_bias_act_fwd_f64;
+    static int conv_fwd(fxb_handle_t h, const double* x, const double* w, const double* b, double* y, const fxb_conv2d_desc* d,
+                        int act, void* ws, size_t wsb, void*, size_t, int* written, fxb_stream_t st) {
+        if (written) *written = 0;
+        return fxb_conv2d_bias_act_fwd_f64(h, x, w, b, y, d, act, ws, wsb, st);
+    }
     static constexpr auto lin_fwd = fxb_linear_fwd_f64;
     static constexpr auto lin_bwd = fxb_linear_bwd_f64;
-    static constexpr auto dgrad = fxb_conv2d_dgrad_act_f64;
-    static constexpr auto wgrad = fxb_conv2d_wgrad_bias_act_f64;
+    static constexpr auto conv_bwd = fxb_conv2d_backward_f64;
     static int ce(fxb_handle_t h, const void* z, const void* t, void* l, void* g, int64_t B, int64_t C, double s, fxb_stream_t st) {
         return fxb_softmax_ce_f64(h, (const double*)z, (const double*)t, (double*)l, (double*)g, B, C, s, st);
     }
@@ -181,7 +199,7 @@ template <typename T>
 int forward_t(Net* n, const void* x, fxb_stream_t st) {
     fxb_handle_t h = reinterpret_cast<fxb_handle_t>(n->ctx);
     for (int i = 0; i < (int)n->layers.size(); ++i) {
-        const NetLayer& L = n->layers[i];
+        NetLayer& L = n->layers[i];
         if (L.kind == FXB_LAYER_FLATTEN) continue;
         const T* in = reinterpret_cast<const T*>(layer_output(n, i - 1, x));
         T* outp = reinterpret_cast<T*>(n->arena + L.act_off);
@@ -189,7 +207,9 @@ int forward_t(Net* n, const void* x, fxb_stream_t st) {
         const T* b = reinterpret_cast<const T*>(n->params) + L.b_off;
         int rc;
         void* ws = n->ws_bytes ? n->arena + n->ws_off : nullptr;
-        if (L.kind == FXB_LAYER_CONV) rc = Api<T>::conv_fwd(h, in, W, b, outp, &L.cd, L.act, ws, n->ws_bytes, st);
+        if (L.kind == FXB_LAYER_CONV)
+            rc = Api<T>::conv_fwd(h, in, W, b, outp, &L.cd, L.act, ws, n->ws_bytes, L.packed_bytes ? n->arena + L.packed_off : nullptr,
+                                  L.packed_bytes, &L.packed_valid, st);
         else rc = Api<T>::lin_fwd(h, in, W, b, outp, n->batch, L.in_c, L.out_c, L.act, st);
         if (rc) return rc;
     }
@@ -213,9 +233,8 @@ int backward_t(Net* n, const void* x, int last, int first, fxb_stream_t st) {
         const T* yact = L.act == FXB_ACT_NONE ? nullptr : outp;
         int rc;
         if (L.kind == FXB_LAYER_CONV) {
-            rc = Api<T>::wgrad(h, in, dy, yact, dW, db, &L.cd, L.act, ws, n->ws_bytes, st);
-            if (rc) return rc;
-            if (dx) rc = Api<T>::dgrad(h, dy, yact, W, dx, &L.cd, L.act, ws, n->ws_bytes, st);
+            rc = Api<T>::conv_bwd(h, in, dy, yact, W, dx, dW, db, &L.cd, L.act, ws, n->ws_bytes,
+                                  L.packed_valid ? n->arena + L.packed_off : nullptr, st);
         } else {
             rc = Api<T>::lin_bwd(h, in, W, yact, dy, dx, dW, db, n->batch, L.in_c, L.out_c, L.act, ws, n->ws_bytes, st);
         }

@@ -3,14 +3,18 @@
 //   dW[o][c][r][s] = sum over (n, oy, ox) of dZ[n][o][oy][ox] * X[n][c][oy*sh + r - ph][ox*sw + s - pw]
 //
 // as a GEMM  D[o][(tap, c)] = sum_k A[o][k] * B[(tap, c)][k]  whose contraction index k runs over
-// the output pixels.  Both operands are prepared "chunk-major" by a pre-pass, hi and lo parts:
-//   A = DZ[g][o][4]            g = (n, oy, ox/4): four consecutive pixels of one output channel
-//   B = XC[t][n][y'][ox/4][c][4], t = (s, cy): for filter column s and row class cy the four
-//       values X[n][c][y'*sh + cy][(ox..ox+3)*sw + s - pw]; tap (r, s) reads rows y' = oy + dyr
-//       of class cy = (r - ph) mod sh, dyr = floor((r - ph) / sh).  Rows above or below the image
-//       are out-of-bounds coordinates of the per-image chunk dimension and read as zeros.
-// so that one K chunk of either operand tile is `rows` x 16 contiguous bytes and a whole 32-pixel
-// stage is one box per operand half (A) or per filter tap of the column tile (B).
+// the images and output pixels.  A 4-wide K chunk is FOUR CONSECUTIVE IMAGES at one pixel, so a
+// filter tap only shifts pixel coordinates (which have no alignment rule for the copy engine) and
+// one copy of the input serves every tap.  Both operands are prepared by a pre-pass, hi and lo parts:
+//   A = DZN[g][oy][ox][o][4]                g = n / 4: dZ of images 4g..4g+3 at one output pixel
+//   B = XN[cls][g][iy][ix][c][4]            the input in padded coordinates (y + ph, x + pw), split into
+//       stride classes cls = (yp % sh, xp % sw) at (iy, ix) = (yp / sh, xp / sw); tap (r, s) pairs output
+//       pixel (oy, ox) with class (r % sh, s % sw) at (oy + r / sh, ox + s / sw).  Cells in the top / left
+//       padding are stored as zeros, cells beyond the bottom / right edge are out-of-bounds coordinates
+//       (read as zeros), and so are the output pixels of a partial box.
+// A 32-deep K stage is a box of bw x bh output pixels (bw * bh = 8) of one image group: one 5-D box per
+// operand half (A) or per filter tap of the column tile (B), each landing in shared memory as
+// [chunk][row][16 bytes], the canonical no-swizzle K-major UMMA layout.
 //
 // A column tile of 128 holds 128/Cb taps of Cb channels (Cb = min(padded C, 128)); each tap has
 // its own operand sub-tile and its own N = Cb slice of the accumulator.  K is split over CTAs
@@ -25,17 +29,18 @@ namespace fxb {
 struct TmaWgradParams {
     CUtensorMap a_hi, a_lo, b_hi, b_lo;
     int tm, tn, splits;       // items = tm * tn * splits, m fastest
-    int stages_total;         // 32-pixel stages over the whole batch
+    int stages_total;         // 32-deep K stages over the whole batch
     int stages_per_split;
     int three_pass;
     int K, C, RS, S;          // output channels, input channels, taps, filter width
-    int Cb;                   // channels per tap sub-tile (16, 32, 64 or 128)
+    int Cb;                   // channels per tap sub-tile (64 or 128)
     int tpt;                  // taps per column tile (128 / Cb)
     int cblocks;              // column tiles per tap (padded C / 128, at least 1)
-    int sh, ph;
-    int PQ, OWQ;              // pixel quads per image / per image row
-    int N;                    // images
-    int imgs_per_stage;       // 1, or 8 / PQ when an image has fewer than 8 quads
+    int sh, sw;
+    int n4;                   // image groups (images / 4, rounded up)
+    int ncls;                 // stride classes (sh * sw)
+    int bw, bh;               // output-pixel box of one stage, bw * bh = 8
+    FastDiv dSpg, dPW;        // stage -> (image group, box row, box column)
     float* out;               // dW (splits == 1) or the partial-sum workspace
     int64_t split_stride;     // elements between the partial results of consecutive splits
 };
@@ -126,19 +131,16 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
             // column tile -> first tap and channel block
             const int tap0 = prm.cblocks > 1 ? nt / prm.cblocks : nt * prm.tpt;
             const int cblk = prm.cblocks > 1 ? nt % prm.cblocks : 0;
-            // this lane's tap: class plane and row displacement
-            int tcoord = 0, dyq = 0;
-            bool tap_ok = false;
+            // this lane's tap: stride class and window displacement
+            int cls_base = prm.ncls * prm.n4, qy = 0, qx = 0;  // a tap beyond the filter reads outside the tensor: zeros
             if (!is_a && jtap < prm.tpt) {
                 const int tap = tap0 + jtap;
-                tap_ok = tap < prm.RS;
-                const int r = tap / prm.S, sx = tap - r * prm.S;
-                const int tt = r - prm.ph;
-                int dyr = tt / prm.sh;
-                if (tt - dyr * prm.sh < 0) --dyr;  // floor division
-                const int cy = tt - dyr * prm.sh;
-                tcoord = (sx * prm.sh + cy) * prm.N;
-                dyq = dyr * prm.OWQ;
+                if (tap < prm.RS) {
+                    const int r = tap / prm.S, sx = tap - r * prm.S;
+                    qy = r / prm.sh;
+                    qx = sx / prm.sw;
+                    cls_base = ((r - qy * prm.sh) * prm.sw + (sx - qx * prm.sw)) * prm.n4;
+                }
             }
             for (int sb = 0; sb < nst && ok; ++sb) {
                 const int s = (int)(pit % Cfg::STAGES);
@@ -156,23 +158,15 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
                 const uint32_t b_lo = b_hi + Cfg::B_BYTES;
                 const int stage = s_begin + sb;
                 if (has_copy) {
+                    uint32_t g, rem, py, px;
+                    prm.dSpg.divmod((uint32_t)stage, g, rem);
+                    prm.dPW.divmod(rem, py, px);
+                    const int oy0 = (int)py * prm.bh, ox0 = (int)px * prm.bw;
                     if (is_a) {
-                        tma_load_3d(is_lo ? a_lo : a_hi, is_lo ? &prm.a_lo : &prm.a_hi, bar, 0, mt * (UMMA_BM / 16),
-                                    stage * TMA_KCH);
+                        tma_load_5d(is_lo ? a_lo : a_hi, is_lo ? &prm.a_lo : &prm.a_hi, bar, 0, mt * (UMMA_BM / 16), ox0, oy0, (int)g);
                     } else {
-                        int n0, q0;
-                        if (prm.imgs_per_stage > 1) {
-                            n0 = stage * prm.imgs_per_stage;
-                            q0 = 0;
-                        } else {
-                            const int gq = stage * TMA_KCH;
-                            n0 = gq / prm.PQ;
-                            q0 = gq - n0 * prm.PQ;
-                        }
-                        // a tap beyond the filter reads a plane index outside the tensor: zeros
-                        const int c3 = tap_ok ? tcoord + n0 : prm.S * prm.sh * prm.N;
-                        tma_load_4d((is_lo ? b_lo : b_hi) + (uint32_t)jtap * sub_bytes, is_lo ? &prm.b_lo : &prm.b_hi, bar, 0,
-                                    cblk * (BN / 16), q0 + dyq, c3);
+                        tma_load_5d((is_lo ? b_lo : b_hi) + (uint32_t)jtap * sub_bytes, is_lo ? &prm.b_lo : &prm.b_hi, bar, 0,
+                                    cblk * (BN / 16), ox0 + qx, oy0 + qy, cls_base + (int)g);
                     }
                 }
                 ++pit;

@@ -243,6 +243,40 @@ class CudaOps:
                                                          self._stream()))
         return (out, db) if want_bias_grad else out
 
+    def conv2d_forward_packing(self, x, w, stride, padding, bias=None, act=None):
+        """conv2d_forward that also packs the layer input for the filter gradient of the same layer.
+        Returns (y, packed) with packed = None when the shape has no packed form."""
+        x, w = self._in(x), self._in(w)
+        d = self._desc(x.shape, w.shape, stride, padding)
+        out = self._get_tensor(self.conv_out_shape(x.shape, w.shape, stride, padding), x)
+        nb = self.lib.fxb_conv2d_fprop_workspace_bytes(self.h, ctypes.byref(d), x.element_size())
+        ws, wsb = self.workspace(nb, x.device)
+        pb = self.lib.fxb_conv2d_packed_input_bytes(self.h, ctypes.byref(d), x.element_size()) if x.dtype == torch.float32 else 0
+        if pb == 0:
+            return self.conv2d_forward(x, w, stride, padding, bias, act), None
+        packed = torch.empty(pb + 256, dtype=torch.uint8, device=x.device)
+        packed = packed[(-packed.data_ptr()) % 256:]
+        written = c_int(0)
+        self._check(self.lib.fxb_conv2d_bias_act_fwd_packing_f32(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.byref(d),
+                                                                 act_code(act), _ptr(ws), wsb, _ptr(packed), pb,
+                                                                 ctypes.byref(written), self._stream()))
+        return out, (packed if written.value else None)
+
+    def conv2d_backward(self, x, dy, w, stride, padding, y=None, act=None, need_dx=True, need_db=True, packed=None):
+        """Conv2dOp::gradient (src/ops/batched.rs:194-217) in one call: (dX, dW, db) of the fused
+        conv + bias + activation layer, with one operand pass over dY."""
+        x, dy, w = self._in(x), self._in(dy), self._in(w)
+        d = self._desc(x.shape, w.shape, stride, padding)
+        dx = self._get_tensor(x.shape, x) if need_dx else None
+        dw = self._get_tensor(w.shape, x)
+        db = self._get_tensor((w.shape[0],), x) if need_db else None
+        nb = self.lib.fxb_conv2d_backward_workspace_bytes(self.h, ctypes.byref(d), x.element_size())
+        ws, wsb = self.workspace(nb, x.device)
+        self._check(self._fn("conv2d_backward", x)(self.h, _ptr(x), _ptr(dy), _ptr(None if y is None else self._in(y)), _ptr(w),
+                                                   _ptr(dx), _ptr(dw), _ptr(db), ctypes.byref(d), act_code(act), _ptr(ws), wsb,
+                                                   _ptr(packed), self._stream()))
+        return dx, dw, db
+
     def _act_fwd(self, x, code):
         x = self._in(x)
         out = self._get_tensor(x.shape, x)

@@ -199,6 +199,30 @@ int fxb_conv2d_wgrad_bias_act_f64(fxb_handle_t h, const double* X, const double*
                                   size_t workspace_bytes, fxb_stream_t stream);
 size_t fxb_conv2d_wgrad_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
 
+/* ---- whole backward of a conv layer: Conv2dOp::gradient (src/ops/batched.rs:194-217) together with the
+ *      activation and bias gradients around it, i.e. fxb_conv2d_wgrad_bias_act + fxb_conv2d_dgrad_act with
+ *      ONE operand pass over dY (dZ = dY * act'(Y) is formed, split and laid out for both kernels at once,
+ *      and the bias gradient falls out of the same pass).  Same results as the two separate calls.
+ *      dX and db may be NULL.  `packed_input` (f32 only, may be NULL): the layer input already packed for
+ *      the filter-gradient kernel by fxb_conv2d_bias_act_fwd_packing_f32 for the same descriptor; without
+ *      it X is packed here.  Workspace: fxb_conv2d_backward_workspace_bytes. ---- */
+int fxb_conv2d_backward_f32(fxb_handle_t h, const float* X, const float* dY, const float* Y, const float* W, float* dX,
+                            float* dW, float* db, const fxb_conv2d_desc* d, int act, void* workspace,
+                            size_t workspace_bytes, const void* packed_input, fxb_stream_t stream);
+int fxb_conv2d_backward_f64(fxb_handle_t h, const double* X, const double* dY, const double* Y, const double* W,
+                            double* dX, double* dW, double* db, const fxb_conv2d_desc* d, int act, void* workspace,
+                            size_t workspace_bytes, const void* packed_input, fxb_stream_t stream);
+size_t fxb_conv2d_backward_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
+/* fxb_conv2d_bias_act_fwd_f32 whose operand pass over X also writes the packed input that the filter
+ * gradient of the same layer reads (so that the backward pass need not read X again): `packed_input` must
+ * hold fxb_conv2d_packed_input_bytes (256-byte aligned; 0 = this shape has no packed form) and stays valid
+ * until the backward call.  *packed_written (may be NULL) tells whether it was written; when it was not,
+ * pass NULL as packed_input to fxb_conv2d_backward_f32.  Y is identical to the plain forward call's. */
+int fxb_conv2d_bias_act_fwd_packing_f32(fxb_handle_t h, const float* X, const float* W, const float* bias, float* Y,
+                                        const fxb_conv2d_desc* d, int act, void* workspace, size_t workspace_bytes,
+                                        void* packed_input, size_t packed_bytes, int* packed_written, fxb_stream_t stream);
+size_t fxb_conv2d_packed_input_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
+
 /* ---- activations: CudaOps::relu/sigmoid/tanh (src/backend/cuda/ops.rs:539-558, :620-628),
  *      kernels/activations.cu:10-48.  Backward replaces the mask/mul chains of
  *      src/ops/unary.rs:254-375: dX = dY * act'(aux), aux = op input for relu, op output for

@@ -313,6 +313,38 @@ def test_conv2d_forward_dx_dw(ops, oracle, dtype, cfg, conv_path):
     assert_parity(dbf, oracle.sum_axes(dz, [3, 2, 0]), "bias grad fused")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cfg", CONV_CASES)
+def test_conv2d_whole_backward_and_packing_forward(ops, oracle, dtype, cfg):
+    """fxb_conv2d_backward (dX, dW, db from one operand pass over dY), with and without the packed input
+    that the packing forward pass leaves behind, against the oracle and against the separate calls."""
+    N, C, H, W, K, R, S, s, p = cfg
+    rng = np.random.default_rng(sum(cfg) + 1)
+    x = rng.standard_normal((N, C, H, W)).astype(dtype)
+    w = kaiming(rng, (K, C, R, S), C * R * S, dtype)
+    bias = (rng.standard_normal(K) * 0.1).astype(dtype)
+    st, pd = (s, s), (p, p)
+    zb = oracle.conv_bias_add(oracle.conv2d(x, w, st, pd), bias)
+    yact = oracle.act_fwd(zb, 1)
+    xt, wt, bt = dev(x), dev(w), dev(bias)
+    y, packed = ops.conv2d_forward_packing(xt, wt, st, pd, bt, "relu")
+    assert_parity(y, yact, "packing forward")
+    assert torch.equal(y, ops.conv2d_forward(xt, wt, st, pd, bt, "relu"))
+    dy = rng.standard_normal(zb.shape).astype(dtype)
+    dz = oracle.act_bwd(dy, zb, 1)
+    yt, dyt = dev(yact), dev(dy)
+    refs = (oracle.deconv2d(dz, w, x.shape, st, pd), oracle.cross_correlation2d(x, dz, w.shape, st, pd), oracle.sum_axes(dz, [3, 2, 0]))
+    for pk in ([None] if packed is None else [None, packed]):
+        got = ops.conv2d_backward(xt, dyt, wt, st, pd, yt, "relu", packed=pk)
+        for g_, r_, nm in zip(got, refs, ("dX", "dW", "db")):
+            assert_parity(g_, r_, f"whole backward {nm} (packed input: {pk is not None})")
+    # no dX wanted (first layer): the filter and bias gradients alone
+    dx0, dw0, db0 = ops.conv2d_backward(xt, dyt, wt, st, pd, yt, "relu", need_dx=False)
+    assert dx0 is None
+    assert_parity(dw0, refs[1], "backward without dX: dW")
+    assert_parity(db0, refs[2], "backward without dX: db")
+
+
 @pytest.mark.parametrize("act", [2, 3])
 def test_conv2d_fused_sigmoid_tanh(ops, oracle, act):
     rng = np.random.default_rng(act)
