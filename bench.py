@@ -55,9 +55,9 @@ def synthetic_batch(rng, n, dtype=np.float32):
     return x, np.eye(10, dtype=dtype)[labels]
 
 
-def workload_config(world):
+def workload_config(world, graph=False):
     """The `config` object of the JSON line (the same for both arms)."""
-    return {"workload": "deep_cnn_train_step_global_batch_1024", "global_batch": GLOBAL_BATCH,
+    return {"launch": "CUDA graph replay" if graph else "eager launches","workload": "deep_cnn_train_step_global_batch_1024", "global_batch": GLOBAL_BATCH,
             "per_gpu_batch": GLOBAL_BATCH // world, "optimizer": "adam", "math": "3xTF32 on tcgen05, f32 accumulate",
             "parallelism": f"dp{world}", "l2": "256 MiB buffer written between timed steps (not timed)",
             "allreduce": "NCCL sum, 2 buckets overlapped with backward" if world > 1 else "none"}
@@ -159,10 +159,10 @@ def torch_cpu_step_rate(sample_images=256, steps=2, warmup=1):
     import torch.nn.functional as F
     rng = np.random.default_rng(SEED)
     chans = [3, 64, 128, 256, 256]
-    ws = [torch.tensor(rng.uniform(-1, 1, (chans[i + 1], chans[i], 3, 3)).astype(np.float32) * np.sqrt(6.0 / (chans[i] * 9)),
+    ws = [torch.tensor((rng.uniform(-1, 1, (chans[i + 1], chans[i], 3, 3)) * np.sqrt(6.0 / (chans[i] * 9))).astype(np.float32),
                        requires_grad=True) for i in range(4)]
     bs = [torch.zeros(chans[i + 1], requires_grad=True) for i in range(4)]
-    wf = torch.tensor(rng.uniform(-1, 1, (10, 4096)).astype(np.float32) * np.sqrt(6.0 / 4096), requires_grad=True)
+    wf = torch.tensor((rng.uniform(-1, 1, (10, 4096)) * np.sqrt(6.0 / 4096)).astype(np.float32), requires_grad=True)
     bf = torch.zeros(10, requires_grad=True)
     params = ws + bs + [wf, bf]
     opt = torch.optim.Adam(params, lr=1e-3)
@@ -403,7 +403,7 @@ def measure_configs(ops, dev, flush, peaks, tf32_peak, f64_peak):
 
 
 # ------------------------------------------------------------------------------------------ the train-step benchmark
-def setup_training(rank, world, local_rank):
+def setup_training(rank, world, local_rank, use_graph=False, batch_override=None):
     import torch
     import torch.distributed as dist
     from ferrox_b200 import build
@@ -417,7 +417,7 @@ def setup_training(rank, world, local_rank):
     from ferrox_b200.cuda_ops import CudaOps
     from ferrox_b200.train import SequentialNet, Trainer, deep_cnn_layers, kaiming_uniform_params
     assert GLOBAL_BATCH % world == 0
-    local_b = GLOBAL_BATCH // world
+    local_b = batch_override or GLOBAL_BATCH // world
     ops = CudaOps(local_rank)
     layers, in_shape = deep_cnn_layers()
     rng = np.random.default_rng(SEED)
@@ -425,9 +425,10 @@ def setup_training(rank, world, local_rank):
     xg, tg = synthetic_batch(rng, GLOBAL_BATCH)
     net = SequentialNet(ops, layers, local_b, in_shape, torch.float32)
     net.set_params(params)
-    tr = Trainer(net, optimizer="adam", lr=1e-3, world_size=world)
-    xs = np.ascontiguousarray(xg[rank * local_b:(rank + 1) * local_b])
-    ts = np.ascontiguousarray(tg[rank * local_b:(rank + 1) * local_b])
+    tr = Trainer(net, optimizer="adam", lr=1e-3, world_size=world, use_graph=use_graph)
+    first = 0 if batch_override else rank * local_b
+    xs = np.ascontiguousarray(xg[first:first + local_b])
+    ts = np.ascontiguousarray(tg[first:first + local_b])
     return dev, ops, net, tr, xs, ts, local_b
 
 
@@ -436,7 +437,7 @@ def run_phases(args, rank, world, local_rank):
     layer's backward, each all-reduce wait, optimizer) and the host time spent issuing it, averaged over the steps."""
     import torch
     import torch.distributed as dist
-    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank)
+    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, batch_override=args.batch)
     x_dev, t_dev = torch.from_numpy(xs).to(dev), torch.from_numpy(ts).to(dev)
     for _ in range(20):
         tr.step(x_dev, t_dev)
@@ -468,7 +469,7 @@ def run_phases(args, rank, world, local_rank):
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank)
+    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, use_graph=args.graph)
     x_pin, t_pin = torch.from_numpy(xs).pin_memory(), torch.from_numpy(ts).pin_memory()
     x_dev, t_dev = x_pin.to(dev), t_pin.to(dev)
     x_stage, t_stage = torch.empty_like(x_dev), torch.empty_like(t_dev)
@@ -501,9 +502,11 @@ def run_ours(args, rank, world, local_rank):
         tr.step(x_dev, t_dev)
 
     def step_e2e():
-        x_stage.copy_(x_pin, non_blocking=True)
-        t_stage.copy_(t_pin, non_blocking=True)
-        loss = tr.step(x_stage, t_stage)
+        xb, tb = tr.input_buffers() if args.graph else (None, None)
+        xb, tb = (x_stage, t_stage) if xb is None else (xb, tb)  # graph mode: copy straight into the graph's inputs
+        xb.copy_(x_pin, non_blocking=True)
+        tb.copy_(t_pin, non_blocking=True)
+        loss = tr.step(xb, tb)
         loss_host.copy_(loss, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -571,7 +574,7 @@ def run_ours(args, rank, world, local_rank):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "dtype": "f32", "data": "synthetic", "config": workload_config(world, args.graph),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_pin.numel() * 4 + t_pin.numel() * 4) * world,
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "loss": loss_value,
@@ -611,6 +614,8 @@ def main():
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--phases", action="store_true", help="print the per-phase timeline of the train step")
     ap.add_argument("--no-configs", action="store_true", help="skip the single-layer / microbenchmark configurations")
+    ap.add_argument("--graph", action="store_true", help="replay the train step from a CUDA graph (captured after three eager steps)")
+    ap.add_argument("--batch", type=int, default=None, help="--phases only: per-GPU batch (e.g. 128, the share of one of 8 GPUs)")
     args = ap.parse_args()
     # keep stdout to the one JSON line: NCCL writes its version banner (NCCL_DEBUG=VERSION/WARN) to stdout
     if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "WARN"):
@@ -629,7 +634,8 @@ def main():
         # convenience: re-launch under torchrun
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__), "--gpus", str(args.gpus),
-               "--steps", str(args.steps), "--warmup", str(args.warmup)] + (["--phases"] if args.phases else [])
+               "--steps", str(args.steps), "--warmup", str(args.warmup)] + (["--phases"] if args.phases else []) + \
+              (["--graph"] if args.graph else [])
         sys.exit(subprocess.call(cmd))
     if args.phases:
         run_phases(args, rank, world, local_rank)

@@ -67,6 +67,7 @@ def _sigs(real):
         "softmax_ce": (I, [H, _P, _P, _P, _P, I64, I64, real, S]),
         "sgd_step": (I, [H, _P, _P, _P, I64, real, real, real, I, real, S]),
         "adam_step": (I, [H, _P, _P, _P, _P, I64, real, real, real, real, real, I64, real, S]),
+        "adam_step_devcount": (I, [H, _P, _P, _P, _P, I64, real, real, real, real, real, _P, real, S]),
         "materialize": (I, [H, _P, _P, POINTER(c_int64), POINTER(c_int64), I, S]),
         "transpose": (I, [H, _P, _P, POINTER(c_int64), I, POINTER(c_int), S]),
         "broadcast_to": (I, [H, _P, POINTER(c_int64), I, _P, POINTER(c_int64), I, S]),

@@ -586,6 +586,38 @@ __global__ void __launch_bounds__(256) adam_kernel(T* __restrict__ p, const T* _
     }
 }
 
+// Adam with the step count in device memory, for a train step that is replayed from a CUDA graph
+// (kernel arguments are frozen at capture time, the bias corrections 1 - beta^t change every step).
+// *step_dev holds the number of steps done so far; the update uses t = *step_dev + 1.  The counter is
+// advanced by the one-thread kernel launched right after (stream order keeps every block of the update
+// on the old value).
+template <typename T> __device__ __forceinline__ T dev_pow(T b, T e);
+template <> __device__ __forceinline__ float dev_pow<float>(float b, float e) { return powf(b, e); }
+template <> __device__ __forceinline__ double dev_pow<double>(double b, double e) { return pow(b, e); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) adam_devcount_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m,
+                                                            T* __restrict__ v, int64_t n, T lr, T b1, T b2, T eps, T wd,
+                                                            const long long* __restrict__ step_dev, T gscale) {
+    const T t = (T)(*step_dev + 1);
+    const T b1p = dev_pow<T>(b1, t), b2p = dev_pow<T>(b2, t);
+    const T bc1 = T(1) - (b1p > T(1e-8) ? b1p : T(1e-8)), bc2 = T(1) - (b2p > T(1e-8) ? b2p : T(1e-8));
+    const T omb1 = T(1) - b1, omb2 = T(1) - b2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        T gi = g[i];
+        if (gscale != T(1)) gi *= gscale;
+        const T mi = m[i] * b1 + gi * omb1;
+        const T vi = v[i] * b2 + (gi * gi) * omb2;
+        m[i] = mi;
+        v[i] = vi;
+        const T den = dev_sqrt<T>(vi / bc2) + eps;
+        const T upd = ((mi / bc1) / den) * lr;
+        const T pi = p[i];
+        p[i] = wd != T(0) ? (pi - upd) - pi * (wd * lr) : pi - upd;
+    }
+}
+__global__ void advance_step_kernel(long long* step_dev) { *step_dev += 1; }
+
 static int flat_grid(const Context* c, int64_t n) {
     return (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)c->sm_count * 8));
 }
@@ -738,6 +770,17 @@ using namespace fxb;
         adam_kernel<T><<<flat_grid(CTX(h), n), 256, 0, ST(s)>>>(p, g, m, v, n, lr, b1, b2, eps, wd, T(1) - b1p,         \
                                                                T(1) - b2p, gscale);                                     \
         return launch_status(CTX(h), "adam_step");                                                                      \
+    }                                                                                                                   \
+    extern "C" int fxb_adam_step_devcount_##SUF(fxb_handle_t h, T* p, const T* g, T* m, T* v, int64_t n, T lr, T b1,    \
+                                                T b2, T eps, T wd, int64_t* step_dev, T gscale, fxb_stream_t s) {       \
+        NEED_HANDLE(h);                                                                                                 \
+        FXB_CHECK_ARG(CTX(h), n >= 0 && step_dev != nullptr && (n == 0 || (p && g && m && v)),                          \
+                      "adam_step_devcount: bad arguments");                                                             \
+        if (n > 0)                                                                                                      \
+            adam_devcount_kernel<T><<<flat_grid(CTX(h), n), 256, 0, ST(s)>>>(                                           \
+                p, g, m, v, n, lr, b1, b2, eps, wd, reinterpret_cast<const long long*>(step_dev), gscale);              \
+        advance_step_kernel<<<1, 1, 0, ST(s)>>>(reinterpret_cast<long long*>(step_dev));                                \
+        return launch_status(CTX(h), "adam_step_devcount", n > 0 ? 2 : 1);                                              \
     }
 
 FXB_STREAM_API(f32, float)

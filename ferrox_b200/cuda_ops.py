@@ -512,3 +512,8 @@ class CudaOps:
     def adam_step_(self, p, g, m, v, step, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, grad_scale=1.0):
         self._check(self._fn("adam_step", p)(self.h, _ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), lr, beta1, beta2, eps,
                                              weight_decay, step, grad_scale, self._stream()))
+
+    def adam_step_devcount_(self, p, g, m, v, step_dev, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, grad_scale=1.0):
+        """Adam::step with the step count in the int64 device tensor `step_dev` (advanced by the call)."""
+        self._check(self._fn("adam_step_devcount", p)(self.h, _ptr(p), _ptr(g), _ptr(m), _ptr(v), p.numel(), lr, beta1, beta2, eps,
+                                                      weight_decay, _ptr(step_dev), grad_scale, self._stream()))

@@ -175,8 +175,12 @@ class Trainer:
     """
 
     def __init__(self, net: SequentialNet, optimizer="sgd", lr=0.01, world_size=1, process_group=None, tail_layers=None,
-                 **opt_kw):
+                 use_graph=False, **opt_kw):
         self.net, self.ops = net, net.ops
+        # use_graph: after three eager steps the whole step (kernels, all-reduces, optimizer) is captured once
+        # into a CUDA graph and replayed from then on; the inputs are copied into fixed buffers first.
+        self.use_graph, self._graph, self._eager_steps = bool(use_graph), None, 0
+        self._x_static = self._t_static = None
         self.optimizer, self.lr, self.opt_kw = optimizer, lr, opt_kw
         self.world, self.pg = int(world_size), process_group
         self.step_count = 0
@@ -184,6 +188,8 @@ class Trainer:
         if optimizer == "adam":
             self.m = torch.zeros_like(net.params)
             self.v = torch.zeros_like(net.params)
+            # graph mode keeps the step count on the device (kernel arguments are frozen in a graph)
+            self.step_dev = torch.zeros(1, dtype=torch.int64, device=net.params.device)
         elif optimizer == "sgd":
             self.mom = torch.zeros_like(net.params) if opt_kw.get("momentum", 0.0) else None
         else:
@@ -193,9 +199,36 @@ class Trainer:
         import torch.distributed as dist
         return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.pg, async_op=True)
 
+    def input_buffers(self):
+        """(x, targets) buffers the captured graph reads, once it exists: a caller that fills them directly
+        (e.g. with its host-to-device copy) and passes them to step() saves the device-to-device copy."""
+        return self._x_static, self._t_static
+
     def step(self, x, targets):
         """x [B_local, ...], targets one-hot [B_local, classes], both on the device.  Returns the
         device tensor holding the (global mean) loss."""
+        if not self.use_graph:
+            return self._step_body(x, targets)
+        if self._graph is None:
+            if self._eager_steps < 3:  # sets kernel attributes, fills the tensor-map cache, creates the communicator
+                self._eager_steps += 1
+                return self._step_body(x, targets)
+            self._x_static, self._t_static = torch.empty_like(x), torch.empty_like(targets)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self._step_body(self._x_static, self._t_static)
+            self.step_count -= 1  # the capture recorded the step without running it
+            self._graph = graph
+        if x.data_ptr() != self._x_static.data_ptr():
+            self._x_static.copy_(x, non_blocking=True)
+        if targets.data_ptr() != self._t_static.data_ptr():
+            self._t_static.copy_(targets, non_blocking=True)
+        self._graph.replay()
+        self.step_count += 1
+        return self.net.loss_slot
+
+    def _step_body(self, x, targets):
         net, ops = self.net, self.ops
         n = net.n_param_layers
         net.forward(x)
@@ -219,7 +252,11 @@ class Trainer:
         net, ops = self.net, self.ops
         self.step_count += 1
         g = net.grads[: net.nparams]
-        if self.optimizer == "adam":
+        if self.optimizer == "adam" and self.use_graph:
+            ops.adam_step_devcount_(net.params, g, self.m, self.v, self.step_dev, lr=self.lr, beta1=self.opt_kw.get("beta1", 0.9),
+                                    beta2=self.opt_kw.get("beta2", 0.999), eps=self.opt_kw.get("eps", 1e-8),
+                                    weight_decay=self.opt_kw.get("weight_decay", 0.0))
+        elif self.optimizer == "adam":
             ops.adam_step_(net.params, g, self.m, self.v, self.step_count, lr=self.lr, beta1=self.opt_kw.get("beta1", 0.9),
                            beta2=self.opt_kw.get("beta2", 0.999), eps=self.opt_kw.get("eps", 1e-8),
                            weight_decay=self.opt_kw.get("weight_decay", 0.0))

@@ -370,6 +370,16 @@ int fxb_adam_step_f64(fxb_handle_t h, double* p, const double* g, double* m, dou
                       double beta1, double beta2, double eps, double weight_decay, int64_t step,
                       double grad_scale, fxb_stream_t stream);
 
+/* The same update with the step count kept in device memory (*step_dev = steps done so far; the update
+ * uses *step_dev + 1 and the call advances the counter), so that a train step captured once in a CUDA
+ * graph can be replayed: kernel arguments are frozen at capture, the bias corrections are not. */
+int fxb_adam_step_devcount_f32(fxb_handle_t h, float* p, const float* g, float* m, float* v, int64_t n, float lr,
+                               float beta1, float beta2, float eps, float weight_decay, int64_t* step_dev,
+                               float grad_scale, fxb_stream_t stream);
+int fxb_adam_step_devcount_f64(fxb_handle_t h, double* p, const double* g, double* m, double* v, int64_t n, double lr,
+                               double beta1, double beta2, double eps, double weight_decay, int64_t* step_dev,
+                               double grad_scale, fxb_stream_t stream);
+
 /* ---- sequential conv/linear network train step: the host-side sequence that Ferrox's layers,
  *      graph and loss issue for one step (examples/common/training.rs:33-81;
  *      src/nn/layers/conv2d.rs:168-214, linear.rs:183-279; src/graph/mod.rs:700-783), expressed

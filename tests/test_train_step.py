@@ -106,3 +106,47 @@ def test_sharded_step_equals_global_step_on_one_gpu(ops, oracle):
     assert_parity(acc[:-1], full.grads[:-1].cpu().numpy(), "summed shard gradients")
     assert_parity(acc[-1] / 2, full.grads[-1].cpu().numpy(), "mean of shard losses")
     full.close(); half.close()
+
+
+def test_graph_replayed_step_equals_eager_step(ops, oracle):
+    """The train step captured once into a CUDA graph (after three eager steps) and replayed gives the same
+    parameters, bit for bit, as eager launches; Adam's step count lives on the device in that mode."""
+    from ferrox_b200.train import SequentialNet, Trainer, deep_cnn_layers, kaiming_uniform_params
+    layers, in_shape = deep_cnn_layers()
+    rng = np.random.default_rng(11)
+    params = kaiming_uniform_params(layers, in_shape, rng, np.float32)
+    batches = [(dev(rng.standard_normal((16, 3, 32, 32)).astype(np.float32)),
+                dev(np.eye(10, dtype=np.float32)[rng.integers(0, 10, 16)])) for _ in range(7)]
+    results = []
+    for use_graph in (False, True):
+        net = SequentialNet(ops, layers, 16, in_shape, torch.float32)
+        net.set_params(params)
+        tr = Trainer(net, optimizer="adam", lr=1e-3, use_graph=use_graph)
+        losses = []
+        for x, t in batches:
+            tr.step(x, t)
+            losses.append(tr.loss_value())
+        assert tr.step_count == len(batches)
+        if use_graph:
+            assert tr._graph is not None and int(tr.step_dev.item()) == len(batches)
+        results.append((losses, net.params.clone()))
+        net.close()
+    assert np.allclose(results[0][0], results[1][0], rtol=1e-6, atol=0)
+    # the device-side bias correction uses powf on the GPU, the eager path pow on the host: allow an ulp or two
+    assert_parity(results[1][1], results[0][1].cpu().numpy(), "parameters after 7 steps, graph vs eager")
+    ops.check_device_status()
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
+def test_adam_with_device_step_count(ops, oracle, dtype):
+    rng = np.random.default_rng(5)
+    n = 5003
+    p, g = rng.standard_normal(n).astype(dtype), rng.standard_normal(n).astype(dtype)
+    pc, m, v = p.copy(), np.zeros(n, dtype), np.zeros(n, dtype)
+    pt, mt, vt = dev(p), dev(np.zeros(n, dtype)), dev(np.zeros(n, dtype))
+    step_dev = torch.zeros(1, dtype=torch.int64, device="cuda:0")
+    for step in range(1, 6):
+        oracle.adam_step(pc, g, m, v, step, wd=0.01)
+        ops.adam_step_devcount_(pt, dev(g), mt, vt, step_dev, weight_decay=0.01)
+    assert int(step_dev.item()) == 5
+    assert_parity(pt, pc, "adam with device step count")
