@@ -229,66 +229,59 @@ __global__ void __launch_bounds__(256) pack_dz_kernel(const float* __restrict__ 
 
 // X NCHW -> XN[cls][g][iy][ix][c][4] (hi and lo): in padded coordinates (yp, xp) = (y + ph, x + pw), class
 // cls = (yp % sh) * sw + xp % sw, cell (iy, ix) = (yp / sh, xp / sw); the four values are images 4g..4g+3,
-// `Cp` channels per cell (zeros beyond C, outside the image and beyond N).  With `slab_hi` the same pass also
-// writes the forward kernel's class slabs S[cls * Q + c/4][n][iy][ix][4].
-// Block = 4 images x 32 channels x RY padded rows; it walks the rows' cells in chunks of 32 through shared
-// memory: reads coalesced along x, writes coalesced along the channels (XN) and along ix (slabs).
-__global__ void __launch_bounds__(256) pack_x_kernel(const float* __restrict__ x, float* __restrict__ xn_hi,
-                                                     float* __restrict__ xn_lo, float* __restrict__ slab_hi,
-                                                     float* __restrict__ slab_lo, int N, int C, int Cp, int H, int W, int Q,
-                                                     int ph, int pw, int Hc, int Wc, int N4, int RY, FastDiv dWp, FastDiv dsh,
-                                                     FastDiv dsw) {
-    __shared__ float t[4][32][33];
+// `Cp` channels per cell (zeros beyond C, outside the image and beyond N).
+// Block = 4 images x 64 channels x a band of RY padded rows, walked in chunks of 32 cells through shared
+// memory: reads coalesced along x; writes ordered by destination address (the cells of a chunk sorted by
+// class, 64 channels = 1 KB per cell), so that a block emits runs of many KB instead of scattered pieces.
+constexpr int XN_CT = 64;  // channels per block
+__global__ void __launch_bounds__(256) pack_xn_kernel(const float* __restrict__ x, float* __restrict__ xn_hi,
+                                                      float* __restrict__ xn_lo, int N, int C, int Cp, int H, int W, int ph,
+                                                      int pw, int Hc, int Wc, int N4, int RY, FastDiv dWp, FastDiv dsh,
+                                                      FastDiv dsw) {
+    __shared__ float t[4][XN_CT][33];
+    __shared__ long long cell_off[32];  // XN float offset of the cell's channel 0, in destination order; -1 = no cell
+    __shared__ int cell_src[32];        // which cell of the chunk that is
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int c0 = blockIdx.x * 32, g = blockIdx.z;
+    const int c0 = blockIdx.x * XN_CT, g = blockIdx.z;
     const int sh = (int)dsh.d, sw = (int)dsw.d;
     const int Wp = Wc * sw, Hp = Hc * sh;
     const int yp0 = blockIdx.y * RY;
     const int rows = min(RY, Hp - yp0);
     const int cells = rows * Wp;
     for (int e0 = 0; e0 < cells; e0 += 32) {
-        {
-            const int e = e0 + lane;
-            uint32_t ry = 0, xp = 0;
-            if (e < cells) dWp.divmod((uint32_t)e, ry, xp);
-            const int y = yp0 + (int)ry - ph, xx = (int)xp - pw;
-            const bool in = e < cells && (unsigned)y < (unsigned)H && (unsigned)xx < (unsigned)W;
-            for (int q = warp; q < 128; q += 8) {
-                const int n4 = q >> 5, cl = q & 31;
-                const int n = 4 * g + n4, c = c0 + cl;
-                t[n4][cl][lane] = (in && n < N && c < C) ? __ldg(x + (((int64_t)n * C + c) * H + y) * W + xx) : 0.f;
+        const int e = e0 + lane;
+        uint32_t ry = 0, xp = 0;
+        if (e < cells) dWp.divmod((uint32_t)e, ry, xp);
+        const int y = yp0 + (int)ry - ph, xx = (int)xp - pw;
+        const bool in = e < cells && (unsigned)y < (unsigned)H && (unsigned)xx < (unsigned)W;
+        for (int q = warp; q < 4 * XN_CT; q += 8) {
+            const int n4 = q / XN_CT, cl = q - n4 * XN_CT;
+            const int n = 4 * g + n4, c = c0 + cl;
+            t[n4][cl][lane] = (in && n < N && c < C) ? __ldg(x + (((int64_t)n * C + c) * H + y) * W + xx) : 0.f;
+        }
+        if (warp == 0) {
+            // destination order: cells sorted by (class, position), i.e. by address
+            uint32_t iy = 0, cy = 0, ix = 0, cx = 0;
+            dsh.divmod((uint32_t)yp0 + ry, iy, cy);
+            dsw.divmod(xp, ix, cx);
+            const int cls = e < cells ? (int)cy * sw + (int)cx : sh * sw;  // cells beyond the band sort last
+            int pos = 0;
+            for (int v = 0; v <= sh * sw; ++v) {
+                const unsigned m = __ballot_sync(0xffffffffu, cls == v);
+                if (v < cls) pos += __popc(m);
+                else if (v == cls) pos += __popc(m & ((1u << lane) - 1u));
             }
+            cell_src[pos] = lane;
+            cell_off[pos] = e < cells ? ((((long long)cls * N4 + g) * Hc + iy) * Wc + ix) * Cp * 4 : -1;
         }
         __syncthreads();
-        if (xn_hi != nullptr) {
-            for (int i = threadIdx.x; i < 1024; i += 256) {
-                const int cl = i & 31, el = i >> 5;
-                const int e = e0 + el, c = c0 + cl;
-                if (e < cells && c < Cp) {
-                    uint32_t ry, xp, iy, cy, ix, cx;
-                    dWp.divmod((uint32_t)e, ry, xp);
-                    dsh.divmod((uint32_t)yp0 + ry, iy, cy);
-                    dsw.divmod(xp, ix, cx);
-                    const int cls = (int)cy * sw + (int)cx;
-                    store_split4(xn_hi, xn_lo, (((((int64_t)cls * N4 + g) * Hc + iy) * Wc + ix) * Cp + c) * 4, t[0][cl][el], t[1][cl][el],
-                                 t[2][cl][el], t[3][cl][el]);
-                }
-            }
-        }
-        if (slab_hi != nullptr) {
-            for (int i = threadIdx.x; i < 1024; i += 256) {
-                const int el = i & 31, rest = i >> 5;
-                const int n4 = rest >> 3, q = rest & 7;
-                const int e = e0 + el, n = 4 * g + n4, qq = (c0 >> 2) + q;
-                if (e < cells && n < N && qq < Q) {
-                    uint32_t ry, xp, iy, cy, ix, cx;
-                    dWp.divmod((uint32_t)e, ry, xp);
-                    dsh.divmod((uint32_t)yp0 + ry, iy, cy);
-                    dsw.divmod(xp, ix, cx);
-                    const int plane = ((int)cy * sw + (int)cx) * Q + qq;
-                    store_split4(slab_hi, slab_lo, ((((int64_t)plane * N + n) * Hc + iy) * Wc + ix) * 4, t[n4][4 * q][el],
-                                 t[n4][4 * q + 1][el], t[n4][4 * q + 2][el], t[n4][4 * q + 3][el]);
-                }
+        for (int i = threadIdx.x; i < 32 * XN_CT; i += 256) {
+            const int pos = i / XN_CT, cl = i - pos * XN_CT;
+            const long long off = cell_off[pos];
+            const int c = c0 + cl;
+            if (off >= 0 && c < Cp) {
+                const int el = cell_src[pos];
+                store_split4(xn_hi, xn_lo, off + (long long)c * 4, t[0][cl][el], t[1][cl][el], t[2][cl][el], t[3][cl][el]);
             }
         }
         __syncthreads();
@@ -700,9 +693,9 @@ static void set_vec_store(TmaConvParams& prm) {
 // described by tensor maps; the caller then takes the cp.async path.
 // phase: which part of the call runs (FPROP_ALL, or one half for timing the two separately).
 enum : int { FPROP_ALL = 0, FPROP_PREPASS_ONLY = 1, FPROP_MAIN_ONLY = 2 };
-static int launch_pack_x(Context* c, const float* X, float* xn_hi, float* xn_lo, float* slab_hi, float* slab_lo,
-                         const ConvGeom& g, int Cp, int Q, int Hc, int Wc, cudaStream_t st);
-// xn_hi / xn_lo (optional): the same pass over X also leaves the filter-gradient kernel's packed input
+static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo, const ConvGeom& g, int Cp, int Hc, int Wc,
+                          cudaStream_t st);
+// xn_hi / xn_lo (optional): the operand pre-pass also leaves the filter-gradient kernel's packed input
 // (xn_cp channels per cell) there, for a backward pass that follows.
 static int conv_fprop_tma(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
                           int act, void* ws, cudaStream_t st, bool* used, int phase = FPROP_ALL, float* xn_hi = nullptr,
@@ -719,18 +712,17 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     if (!encode_filter_maps(prm, w.b_hi, w.b_lo, l.rows_pad, g.RS * l.Q, bn)) return FXB_OK;
     *used = true;
     if (phase != FPROP_MAIN_ONLY) {
-        int rc;
-        if (xn_hi != nullptr) {
-            rc = launch_pack_x(c, X, xn_hi, xn_lo, w.a_hi, w.a_lo, g, xn_cp, l.Q, l.Hc, l.Wc, st);
-        } else {
-            const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
-            const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
-            split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
-                                                                      total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
-                                                                      FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
-            rc = launch_status(c, "split_image_to_class_slabs_kernel");
-        }
+        const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
+        const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
+        split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
+                                                                  total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
+                                                                  FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
+        int rc = launch_status(c, "split_image_to_class_slabs_kernel");
         if (rc) return rc;
+        if (xn_hi != nullptr) {
+            rc = launch_pack_xn(c, X, xn_hi, xn_lo, g, xn_cp, l.Hc, l.Wc, st);
+            if (rc) return rc;
+        }
         FilterClassBase fc{};
         const int ftotal = g.RS * l.Q * l.rows_pad;
         const int fblocks = std::max(1, std::min((ftotal + 255) / 256, c->sm_count * 8));
@@ -1018,7 +1010,8 @@ static int conv_dgrad_impl(Context* c, const T* dY, const T* Yact, const T* W, T
 
 // ---- small-C filter gradient: partial sums of every block, then a fixed-order finish ---------
 static int smallc_wgrad_blocks(const Context* c, int64_t npix) {
-    return (int)std::max<int64_t>(1, std::min<int64_t>((npix + 31) / 32, (int64_t)c->sm_count * 8));
+    // at least eight 32-pixel tiles per block (the finish kernels add one row per block), at most eight blocks per SM
+    return (int)std::max<int64_t>(1, std::min<int64_t>((npix + 255) / 256, (int64_t)c->sm_count * 8));
 }
 static size_t smallc_wgrad_bytes(const Context* c, int64_t npix, size_t elem) {
     const size_t blocks = (size_t)smallc_wgrad_blocks(c, npix);
@@ -1096,18 +1089,17 @@ static TmaWgradLayout tma_wgrad_layout(const Context* c, const ConvGeom& g) {
     return l;
 }
 
-// x -> XN (and, with slab pointers, the forward kernel's class slabs) in one pass.
-static int launch_pack_x(Context* c, const float* X, float* xn_hi, float* xn_lo, float* slab_hi, float* slab_lo,
-                         const ConvGeom& g, int Cp, int Q, int Hc, int Wc, cudaStream_t st) {
+// x -> XN, the packed input of the filter-gradient kernel.
+static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo, const ConvGeom& g, int Cp, int Hc, int Wc,
+                          cudaStream_t st) {
     const int n4 = (g.N + 3) / 4;
     const int Wp = Wc * g.sw, Hp = Hc * g.sh;
-    const int chans = std::max(xn_hi ? Cp : 0, slab_hi ? Q * 4 : 0);
     const int ry = std::max(1, std::min(Hp, (256 + Wp - 1) / Wp));  // about eight 32-cell chunks per block
     if (n4 > 65535 || (Hp + ry - 1) / ry > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Conv2D batch too large for the packed operand pass");
-    dim3 grid((chans + 31) / 32, (Hp + ry - 1) / ry, n4);
-    pack_x_kernel<<<grid, 256, 0, st>>>(X, xn_hi, xn_lo, slab_hi, slab_lo, g.N, g.C, Cp, g.H, g.W, Q, g.ph, g.pw, Hc, Wc, n4, ry,
-                                        FastDiv((uint32_t)Wp), FastDiv((uint32_t)g.sh), FastDiv((uint32_t)g.sw));
-    return launch_status(c, "pack_x_kernel");
+    dim3 grid((Cp + XN_CT - 1) / XN_CT, (Hp + ry - 1) / ry, n4);
+    pack_xn_kernel<<<grid, 256, 0, st>>>(X, xn_hi, xn_lo, g.N, g.C, Cp, g.H, g.W, g.ph, g.pw, Hc, Wc, n4, ry, FastDiv((uint32_t)Wp),
+                                         FastDiv((uint32_t)g.sh), FastDiv((uint32_t)g.sw));
+    return launch_status(c, "pack_xn_kernel");
 }
 // dY (* act'(Y)) -> DZN (+ channel slabs for the input gradient) (+ bias gradient).
 static int launch_pack_dz(Context* c, const float* dY, const float* Yact, float* dzn_hi, float* dzn_lo, float* slab_hi,
@@ -1220,7 +1212,7 @@ static int conv_wgrad_tma(Context* c, const float* X, const float* dY, const flo
     int rc = launch_pack_dz(c, dY, Yact, w.dz_hi, w.dz_lo, nullptr, nullptr, w.dbpart, db, g, l, act, st);
     if (rc) return rc;
     if (own_xn) {
-        rc = launch_pack_x(c, X, w.xn_hi, w.xn_lo, nullptr, nullptr, g, l.Cp, 0, l.Hc, l.Wc, st);
+        rc = launch_pack_xn(c, X, w.xn_hi, w.xn_lo, g, l.Cp, l.Hc, l.Wc, st);
         if (rc) return rc;
     }
     bool launched = false;
@@ -1347,7 +1339,7 @@ static int conv_backward_impl(Context* c, const T* X, const T* dY, const T* Yact
             rc = launch_pack_dz(c, dY, Yact, w.dz_hi, w.dz_lo, sw.a_hi, sw.a_lo, w.dbpart, db, g, l, act, st);
             if (rc) return rc;
             if (own_xn) {
-                rc = launch_pack_x(c, X, w.xn_hi, w.xn_lo, nullptr, nullptr, g, l.Cp, 0, l.Hc, l.Wc, st);
+                rc = launch_pack_xn(c, X, w.xn_hi, w.xn_lo, g, l.Cp, l.Hc, l.Wc, st);
                 if (rc) return rc;
             }
             bool launched = false;
