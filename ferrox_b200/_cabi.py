@@ -85,6 +85,7 @@ _COMMON = {
     "fxb_status_string": (c_char_p, [c_int]),
     "fxb_set_math_mode": (c_int, [c_void_p, c_int]),
     "fxb_set_operand_path": (c_int, [c_void_p, c_int]),
+    "fxb_set_accumulate_stages": (c_int, [c_void_p, c_int]),
     "fxb_set_sigmoid_grad_mode": (c_int, [c_void_p, c_int]),
     "fxb_check_device_status": (c_int, [c_void_p, c_void_p]),
     "fxb_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_void_p]),

@@ -130,6 +130,14 @@ extern "C" int fxb_set_operand_path(fxb_handle_t h, int path) {
     return FXB_OK;
 }
 
+extern "C" int fxb_set_accumulate_stages(fxb_handle_t h, int stages) {
+    if (h == nullptr) return fail(nullptr, FXB_ERR_INVALID_ARGUMENT, "null ferrox_b200 handle");
+    Context* c = reinterpret_cast<Context*>(h);
+    if (stages != 1 && stages != 2 && stages != 4) return fail(c, FXB_ERR_INVALID_ARGUMENT, "accumulate stages must be 1, 2 or 4");
+    c->drain_group = stages;
+    return FXB_OK;
+}
+
 extern "C" int fxb_set_sigmoid_grad_mode(fxb_handle_t h, int math_mode) {
     if (h == nullptr) return fail(nullptr, FXB_ERR_INVALID_ARGUMENT, "null ferrox_b200 handle");
     reinterpret_cast<Context*>(h)->sigmoid_grad_math = math_mode ? 1 : 0;

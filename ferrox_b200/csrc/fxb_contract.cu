@@ -22,6 +22,18 @@ __global__ void splitk_reduce_kernel(const T* __restrict__ part, T* __restrict__
     }
 }
 
+// The same for a split forward convolution: out[n][k][p] = act(sum_z part[z][...] + bias[k]).
+__global__ void __launch_bounds__(256) splitk_bias_act_kernel(const float* __restrict__ part, float* __restrict__ out, int64_t n,
+                                                              int64_t stride, int splits, const float* __restrict__ bias,
+                                                              FastDiv dP, int K, int act) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = part[i];
+        for (int z = 1; z < splits; ++z) acc += part[(int64_t)z * stride + i];
+        if (bias != nullptr) acc += __ldg(bias + dP.div((uint32_t)i) % (uint32_t)K);
+        out[i] = act_apply<float>(acc, act);
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // Pre-split kernels of the copy-engine convolution path (f32).  They rewrite an operand once into
 // TF32 "hi" (round to nearest) and exact remainder "lo" arrays whose 4-element K chunks are
@@ -189,16 +201,24 @@ __global__ void __launch_bounds__(256) pack_dz_kernel(const float* __restrict__ 
     __shared__ float t[4][32][33];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int p0 = blockIdx.x * 32, o0 = blockIdx.y * 32, g = blockIdx.z;
-    for (int q = warp; q < 128; q += 8) {
+    // all loads are issued before the first value is used (up to 32 independent loads in flight per thread)
+    float vd[16], vy[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int q = warp + 8 * j;
         const int n4 = q >> 5, ol = q & 31;
         const int n = 4 * g + n4, o = o0 + ol, p = p0 + lane;
-        float v = 0.f;
-        if (n < N && o < K && p < P) {
-            const int64_t src = ((int64_t)n * K + o) * P + p;
-            v = __ldg(dy + src);
-            if (yact) v *= act_grad_factor<float>(__ldg(yact + src), act, sig_math);
-        }
-        t[n4][ol][lane] = v;
+        const bool in = n < N && o < K && p < P;
+        const int64_t src = ((int64_t)n * K + o) * P + p;
+        vd[j] = in ? __ldg(dy + src) : 0.f;
+        vy[j] = (in && yact != nullptr) ? __ldg(yact + src) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int q = warp + 8 * j;
+        float v = vd[j];
+        if (yact) v *= act_grad_factor<float>(vy[j], act, sig_math);
+        t[q >> 5][q & 31][lane] = v;
     }
     __syncthreads();
     if (dbpart != nullptr && warp == 0 && o0 + lane < K) {
@@ -254,10 +274,20 @@ __global__ void __launch_bounds__(256) pack_xn_kernel(const float* __restrict__ 
         if (e < cells) dWp.divmod((uint32_t)e, ry, xp);
         const int y = yp0 + (int)ry - ph, xx = (int)xp - pw;
         const bool in = e < cells && (unsigned)y < (unsigned)H && (unsigned)xx < (unsigned)W;
-        for (int q = warp; q < 4 * XN_CT; q += 8) {
+        // all loads of the chunk are issued before the first value is used (32 independent loads in flight per thread)
+        float v[4 * XN_CT / 8];
+#pragma unroll
+        for (int j = 0; j < 4 * XN_CT / 8; ++j) {
+            const int q = warp + 8 * j;
             const int n4 = q / XN_CT, cl = q - n4 * XN_CT;
             const int n = 4 * g + n4, c = c0 + cl;
-            t[n4][cl][lane] = (in && n < N && c < C) ? __ldg(x + (((int64_t)n * C + c) * H + y) * W + xx) : 0.f;
+            v[j] = (in && n < N && c < C) ? __ldg(x + (((int64_t)n * C + c) * H + y) * W + xx) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4 * XN_CT / 8; ++j) {
+            const int q = warp + 8 * j;
+            const int n4 = q / XN_CT, cl = q - n4 * XN_CT;
+            t[n4][cl][lane] = v[j];
         }
         if (warp == 0) {
             // destination order: cells sorted by (class, position), i.e. by address
@@ -288,20 +318,34 @@ __global__ void __launch_bounds__(256) pack_xn_kernel(const float* __restrict__ 
     }
 }
 
-// out[o] = sum over b of part[b][o], b in a fixed order: eight interleaved running sums per output,
-// combined as a fixed tree, so the result does not depend on scheduling.
+// out[o] = sum over b of part[b][o], b in a fixed order: block = 8 outputs x 32 row lanes, every lane keeps four
+// interleaved running sums (four independent loads in flight), combined as a fixed tree, so the result does
+// not depend on scheduling.
 __global__ void __launch_bounds__(256) partial_rows_sum_kernel(const float* __restrict__ part, float* __restrict__ out, int K,
                                                                int rows) {
-    __shared__ float red[8][32];
-    const int ol = threadIdx.x & 31, bl = threadIdx.x >> 5;
-    const int o = blockIdx.x * 32 + ol;
-    float acc = 0.f;
-    if (o < K)
-        for (int b = bl; b < rows; b += 8) acc += __ldg(part + (int64_t)b * K + o);
-    red[bl][ol] = acc;
+    __shared__ float red[32][9];
+    const int ol = threadIdx.x & 7, bl = threadIdx.x >> 3;
+    const int o = blockIdx.x * 8 + ol;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    if (o < K) {
+        int b = bl;
+        for (; b + 96 < rows; b += 128) {
+            a0 += __ldg(part + (int64_t)b * K + o);
+            a1 += __ldg(part + (int64_t)(b + 32) * K + o);
+            a2 += __ldg(part + (int64_t)(b + 64) * K + o);
+            a3 += __ldg(part + (int64_t)(b + 96) * K + o);
+        }
+        for (; b < rows; b += 32) a0 += __ldg(part + (int64_t)b * K + o);
+    }
+    red[bl][ol] = (a0 + a1) + (a2 + a3);
     __syncthreads();
-    if (bl == 0 && o < K)
-        out[o] = ((red[0][ol] + red[1][ol]) + (red[2][ol] + red[3][ol])) + ((red[4][ol] + red[5][ol]) + (red[6][ol] + red[7][ol]));
+    if (bl == 0 && o < K) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int w = 0; w < 32; w += 4) {
+            s[0] += red[w][ol]; s[1] += red[w + 1][ol]; s[2] += red[w + 2][ol]; s[3] += red[w + 3][ol];
+        }
+        out[o] = (s[0] + s[1]) + (s[2] + s[3]);
+    }
 }
 
 template <typename T>
@@ -598,12 +642,29 @@ static TmaFpropLayout tma_fprop_layout(const ConvGeom& g) {
 }
 static bool tma_stride_ok(const ConvGeom& g) { return g.sh * g.sw <= 16; }
 
-static size_t fprop_split_bytes(const ConvGeom& g) {
+// Split-K plan of the tensor-map forward convolution: with fewer tiles than half the SMs, the K stages of a
+// tile are divided among several CTAs (partial sums in the workspace, added in split order afterwards).
+struct FpropSplit { int splits, stages_per_split; };
+static FpropSplit fprop_split_plan(const Context* c, const ConvGeom& g) {
+    const PatchPlan pp = plan_patch(g.OH, g.OW);
+    const int bn = tile_cols(g.K);
+    const int tiles = (g.N + pp.ni - 1) / pp.ni * pp.PH * pp.PW * ((g.K + bn - 1) / bn);
+    const int stages = (g.RS * ((g.C + 3) / 4) + TMA_KCH - 1) / TMA_KCH;
+    FpropSplit f{1, stages};
+    if (tiles * 2 > c->sm_count || stages < 8) return f;
+    const int want = std::max(1, std::min(c->sm_count / tiles, stages / 4));
+    f.stages_per_split = (stages + want - 1) / want;
+    f.splits = (stages + f.stages_per_split - 1) / f.stages_per_split;
+    return f;
+}
+static size_t fprop_split_bytes(const Context* c, const ConvGeom& g) {
     const int64_t C4 = (g.C + 3) / 4;
     size_t need = carve_split_ws(nullptr, (int64_t)g.N * C4 * g.HW * 4, (int64_t)g.K * g.RS * C4 * 4).bytes;
     if (tma_stride_ok(g)) {
         const TmaFpropLayout l = tma_fprop_layout(g);
-        need = std::max(need, carve_split_ws(nullptr, l.image_floats, l.filter_floats).bytes);
+        const FpropSplit f = fprop_split_plan(c, g);
+        const size_t part = f.splits > 1 ? align_up256((size_t)f.splits * g.N * g.K * g.P * 4) : 0;
+        need = std::max(need, align_up256(carve_split_ws(nullptr, l.image_floats, l.filter_floats).bytes) + part);
     }
     return need;
 }
@@ -642,7 +703,7 @@ static int launch_tma_bn(Context* c, const TmaConvParams& prm, cudaStream_t st) 
         FXB_CUDA_OK(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set[c->device & 63] = true;
     }
-    const long long items = (long long)prm.tm * prm.tn;
+    const long long items = (long long)prm.tm * prm.tn * prm.ncls * prm.splits;
     const int grid = (int)std::min<long long>(items, c->sm_count);  // persistent: one CTA per SM
     kern<<<grid, TMA_CONV_THREADS, Cfg::SMEM_BYTES, st>>>(prm, c->d_status);
     return launch_status(c, "umma_tma_conv_kernel");
@@ -737,12 +798,25 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     prm.ncls = 1;
     prm.kchunks[0] = g.RS * l.Q;
     prm.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
+    prm.drain_group = c->drain_group;
     prm.dQ.init((uint32_t)l.Q); prm.dS[0].init((uint32_t)g.S);
     prm.Q = l.Q; prm.sh = g.sh; prm.sw = g.sw; prm.dir = 1; prm.by[0] = 0; prm.bx[0] = 0; prm.planes = l.planes;
     prm.out = Y; prm.bias = bias; prm.act = act;
     prm.img_stride = (int64_t)g.K * g.P; prm.nstr = g.P; prm.goff[0] = 0; prm.gys = g.OW; prm.gxs = 1;
+    const FpropSplit fs = fprop_split_plan(c, g);
+    if (fs.splits > 1) {
+        prm.splits = fs.splits;
+        prm.stages_per_split = fs.stages_per_split;
+        prm.split_stride = (int64_t)g.N * g.K * g.P;
+        prm.out = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up256(w.bytes));
+    }
     set_vec_store(prm);
-    return launch_tma(c, prm, bn, st);
+    int rc = launch_tma(c, prm, bn, st);
+    if (rc || fs.splits == 1) return rc;
+    const int64_t n = prm.split_stride;
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)c->sm_count * 8);
+    splitk_bias_act_kernel<<<blocks, 256, 0, st>>>(prm.out, Y, n, n, fs.splits, bias, FastDiv((uint32_t)g.P), g.K, act);
+    return launch_status(c, "splitk_bias_act_kernel");
 }
 
 static int conv_fprop_async(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
@@ -780,7 +854,7 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         if constexpr (sizeof(T) == 4) {
             bool used = false;
             if (c->operand_path == FXB_PATH_AUTO && ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 &&
-                ws_bytes >= fprop_split_bytes(g) && g.CRS > SMALLC_K)
+                ws_bytes >= fprop_split_bytes(c, g) && g.CRS > SMALLC_K)
                 rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, phase);
             if (rc) return rc;
             if (used) return FXB_OK;
@@ -799,7 +873,7 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         // shapes it cannot describe, by cp.async); without one the kernel gathers and splits them on
         // the fly (same results).
         if (c->operand_path != FXB_PATH_GATHER && ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 &&
-            ws_bytes >= fprop_split_bytes(g)) {
+            ws_bytes >= fprop_split_bytes(c, g)) {
             if (c->operand_path != FXB_PATH_CP_ASYNC) {
                 bool used = false;
                 rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used);
@@ -870,6 +944,7 @@ static int conv_dgrad_tma(Context* c, const float* dY, const float* Yact, const 
             q.ncls = 1;
             q.kchunks[0] = chunks;
             q.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
+            q.drain_group = c->drain_group;
             q.dQ.init((uint32_t)K4); q.dS[0].init((uint32_t)Sc);
             q.Q = K4; q.sh = 1; q.sw = 1; q.dir = -1; q.by[0] = cl.oy0; q.bx[0] = cl.ox0; q.planes = K4;
             q.out = dX; q.bias = nullptr; q.act = FXB_ACT_NONE;
@@ -1023,9 +1098,16 @@ __global__ void __launch_bounds__(256) smallc_db_finish_kernel(const T* __restri
     __shared__ T red[8][32];
     const int el = threadIdx.x & 31, bl = threadIdx.x >> 5;
     const int o = blockIdx.x * 32 + el;
-    T acc = T(0);
-    for (int b = bl; b < rows; b += 8) acc += __ldg(dbpart + (int64_t)b * 64 + o);
-    red[bl][el] = acc;
+    T a0 = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+    int b = bl;
+    for (; b + 24 < rows; b += 32) {  // four independent loads in flight
+        a0 += __ldg(dbpart + (int64_t)b * 64 + o);
+        a1 += __ldg(dbpart + (int64_t)(b + 8) * 64 + o);
+        a2 += __ldg(dbpart + (int64_t)(b + 16) * 64 + o);
+        a3 += __ldg(dbpart + (int64_t)(b + 24) * 64 + o);
+    }
+    for (; b < rows; b += 8) a0 += __ldg(dbpart + (int64_t)b * 64 + o);
+    red[bl][el] = (a0 + a1) + (a2 + a3);
     __syncthreads();
     if (bl == 0 && o < K)
         db[o] = ((red[0][el] + red[1][el]) + (red[2][el] + red[3][el])) + ((red[4][el] + red[5][el]) + (red[6][el] + red[7][el]));
@@ -1112,7 +1194,7 @@ static int launch_pack_dz(Context* c, const float* dY, const float* Yact, float*
     int rc = launch_status(c, "pack_dz_kernel");
     if (rc) return rc;
     if (db) {
-        partial_rows_sum_kernel<<<(g.K + 31) / 32, 256, 0, st>>>(dbpart, db, g.K, l.db_rows);
+        partial_rows_sum_kernel<<<(g.K + 7) / 8, 256, 0, st>>>(dbpart, db, g.K, l.db_rows);
         rc = launch_status(c, "partial_rows_sum_kernel");
     }
     return rc;
@@ -1142,6 +1224,7 @@ static int launch_wgrad_tma(Context* c, const float* dz_hi, const float* dz_lo, 
     prm.tm = l.tm; prm.tn = l.tn; prm.splits = l.splits;
     prm.stages_total = l.stages_total; prm.stages_per_split = l.stages_per_split;
     prm.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
+    prm.drain_group = c->drain_group;
     prm.K = g.K; prm.C = g.C; prm.RS = g.RS; prm.S = g.S;
     prm.Cb = l.Cb; prm.tpt = l.tpt; prm.cblocks = l.cblocks;
     prm.sh = g.sh; prm.sw = g.sw; prm.n4 = l.n4; prm.ncls = l.ncls; prm.bw = l.bw; prm.bh = l.bh;
@@ -1295,7 +1378,7 @@ static int conv_fprop_packing(Context* c, const float* X, const float* W, const 
     const size_t need = conv_packed_bytes(c, g);
     if (packed != nullptr && need > 0 && packed_bytes >= need && (reinterpret_cast<uintptr_t>(packed) & 255) == 0 && X && W && Y &&
         act >= FXB_ACT_NONE && act <= FXB_ACT_TANH && c->operand_path == FXB_PATH_AUTO && ws != nullptr &&
-        (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes >= fprop_split_bytes(g)) {
+        (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && ws_bytes >= fprop_split_bytes(c, g)) {
         const TmaWgradLayout l = tma_wgrad_layout(c, g);
         float* xn_hi = static_cast<float*>(packed);
         float* xn_lo = reinterpret_cast<float*>(static_cast<char*>(packed) + align_up256((size_t)l.xn_floats * 4));
@@ -1360,9 +1443,19 @@ static int conv_backward_impl(Context* c, const T* X, const T* dY, const T* Yact
     return conv_dgrad_impl<T>(c, dY, Yact, W, dX, d, act, ws, ws_bytes, st);
 }
 
+// Batch rows per partial-sum chunk of the skinny dW kernel: small enough for about two CTAs per SM, a power of
+// two between 8 and SKINNY_ROWS.
+static int skinny_rows_per_chunk(const Context* c, int64_t B, int64_t in) {
+    const int64_t colblocks = (in + 255) / 256;
+    const int64_t want_chunks = std::max<int64_t>(1, (2 * (int64_t)c->sm_count + colblocks - 1) / colblocks);
+    int rows = SKINNY_ROWS;
+    while (rows > 8 && (B + rows - 1) / rows < want_chunks) rows >>= 1;
+    return rows;
+}
 template <typename T>
-static size_t skinny_bwd_bytes(int64_t B, int64_t in, int64_t out) {
-    const int64_t chunks = (B + SKINNY_ROWS - 1) / SKINNY_ROWS;
+static size_t skinny_bwd_bytes(const Context* c, int64_t B, int64_t in, int64_t out) {
+    const int rows = skinny_rows_per_chunk(c, B, in);
+    const int64_t chunks = (B + rows - 1) / rows;
     return chunks > 1 ? (size_t)(chunks * out * in + chunks * out) * sizeof(T) : 0;
 }
 
@@ -1388,16 +1481,17 @@ static int linear_bwd_impl(Context* c, const T* X, const T* W, const T* Y, const
     FXB_CHECK_ARG(c, X && W && dY && dW, "Linear backward got a null buffer");
     FXB_CHECK_ARG(c, act == FXB_ACT_NONE || Y != nullptr, "Fused activation backward needs the layer output");
     const T* aux = act == FXB_ACT_NONE ? nullptr : Y;
-    // grid limits of the three kernels: chunks of 128 rows and blocks of 256 columns in grid.y (<= 65535)
-    if (out <= SKINNY_MAXO && fits_i32(B) && fits_i32(in) && B <= 65535 * (int64_t)SKINNY_ROWS && in <= 65535 * (int64_t)256) {
-        const int chunks = (int)((B + SKINNY_ROWS - 1) / SKINNY_ROWS);
-        const size_t need = skinny_bwd_bytes<T>(B, in, out);
+    // grid limits of the three kernels: chunks of at least 8 rows and blocks of 256 columns in grid.y (<= 65535)
+    if (out <= SKINNY_MAXO && fits_i32(B) && fits_i32(in) && B <= 65535 * (int64_t)8 && in <= 65535 * (int64_t)256) {
+        const int rpc = skinny_rows_per_chunk(c, B, in);
+        const int chunks = (int)((B + rpc - 1) / rpc);
+        const size_t need = skinny_bwd_bytes<T>(c, B, in, out);
         if (chunks == 1 || (ws != nullptr && ws_bytes >= need)) {
             T* part = chunks == 1 ? dW : static_cast<T*>(ws);
             T* dbpart = db == nullptr ? nullptr : (chunks == 1 ? db : part + (size_t)chunks * out * in);
             dim3 grid((unsigned)((in + 255) / 256), (unsigned)chunks);
             skinny_linear_dw_kernel<T><<<grid, 256, 0, st>>>(X, dY, aux, part, dbpart, (int)B, (int)in, (int)out, act,
-                                                             c->sigmoid_grad_math);
+                                                             c->sigmoid_grad_math, rpc);
             int rc = launch_status(c, "skinny_linear_dw_kernel");
             if (rc) return rc;
             if (chunks > 1) {
@@ -1535,7 +1629,7 @@ extern "C" size_t fxb_gemm_workspace_bytes(fxb_handle_t h, int64_t M, int64_t N,
 extern "C" size_t fxb_linear_bwd_workspace_bytes(fxb_handle_t h, int64_t B, int64_t in, int64_t out, size_t elem) {
     if (!h || B <= 0 || in <= 0 || out <= 0) return 0;
     size_t need = split_ws_upper(CTX(h), out, in, B, out * in, (int)out, 0, elem);
-    if (out <= SKINNY_MAXO) need = std::max(need, elem == 8 ? skinny_bwd_bytes<double>(B, in, out) : skinny_bwd_bytes<float>(B, in, out));
+    if (out <= SKINNY_MAXO) need = std::max(need, elem == 8 ? skinny_bwd_bytes<double>(CTX(h), B, in, out) : skinny_bwd_bytes<float>(CTX(h), B, in, out));
     return need;
 }
 extern "C" int fxb_conv2d_fprop_prepass_f32(fxb_handle_t h, const float* X, const float* W, const fxb_conv2d_desc* d,
@@ -1562,7 +1656,7 @@ extern "C" size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t h, const fxb_con
     if (!h || !d || elem != 4) return 0;
     ConvGeom g;
     if (make_geom(CTX(h), d, g) != FXB_OK) return 0;
-    return fprop_split_bytes(g);
+    return fprop_split_bytes(CTX(h), g);
 }
 extern "C" size_t fxb_conv2d_dgrad_workspace_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
     if (!h || !d || elem != 4) return 0;

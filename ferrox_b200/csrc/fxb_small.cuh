@@ -73,17 +73,17 @@ __global__ void __launch_bounds__(256) skinny_linear_dx_kernel(const T* __restri
     dX[(int64_t)b * in + i] = acc;
 }
 
-// Partial dW / db over one chunk of `rows_per_chunk` batch rows: part[chunk][o][i] = sum_b dZ[b][o] * X[b][i],
+// Partial dW / db over one chunk of `rows_per_chunk` (<= SKINNY_ROWS) batch rows: part[chunk][o][i] = sum_b dZ[b][o] * X[b][i],
 // dbpart[chunk][o] = sum_b dZ[b][o]; grid (ceil(in/256), chunks).  The chunks are added in order afterwards.
 constexpr int SKINNY_ROWS = 128;
 template <typename T>
 __global__ void __launch_bounds__(256) skinny_linear_dw_kernel(const T* __restrict__ X, const T* __restrict__ dY,
                                                                const T* __restrict__ Yact, T* __restrict__ part,
                                                                T* __restrict__ dbpart, int B, int in, int out, int act,
-                                                               int sig_math) {
+                                                               int sig_math, int rows_per_chunk) {
     __shared__ T dz[SKINNY_ROWS * SKINNY_MAXO];
-    const int b0 = blockIdx.y * SKINNY_ROWS;
-    const int rows = min(SKINNY_ROWS, B - b0);
+    const int b0 = blockIdx.y * rows_per_chunk;
+    const int rows = min(rows_per_chunk, B - b0);
     for (int e = threadIdx.x; e < rows * out; e += blockDim.x) {
         T v = __ldg(dY + (int64_t)b0 * out + e);
         if (Yact) v *= act_grad_factor<T>(__ldg(Yact + (int64_t)b0 * out + e), act, sig_math);
@@ -100,8 +100,20 @@ __global__ void __launch_bounds__(256) skinny_linear_dw_kernel(const T* __restri
     T acc[SKINNY_MAXO];
 #pragma unroll
     for (int o = 0; o < SKINNY_MAXO; ++o) acc[o] = T(0);
-    for (int r = 0; r < rows; ++r) {
-        const T xv = __ldg(X + (int64_t)(b0 + r) * in + i);
+    const T* xp = X + (int64_t)b0 * in + i;
+    int r = 0;
+    for (; r + 8 <= rows; r += 8) {  // eight row loads in flight, then the FMAs in row order
+        T xv[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) xv[u] = __ldg(xp + (int64_t)(r + u) * in);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int o = 0; o < SKINNY_MAXO; ++o)
+                if (o < out) acc[o] += dz[(r + u) * out + o] * xv[u];
+    }
+    for (; r < rows; ++r) {
+        const T xv = __ldg(xp + (int64_t)r * in);
 #pragma unroll
         for (int o = 0; o < SKINNY_MAXO; ++o)
             if (o < out) acc[o] += dz[r * out + o] * xv;
@@ -259,9 +271,16 @@ __global__ void __launch_bounds__(256) smallc_wgrad_finish_kernel(const T* __res
     __shared__ T red[8][32];
     const int el = threadIdx.x & 31, bl = threadIdx.x >> 5;
     const int e = blockIdx.x * 32 + el;  // index into [64][SMALLC_K]
-    T acc = T(0);
-    for (int b = bl; b < rows; b += 8) acc += __ldg(part + (int64_t)b * 64 * SMALLC_K + e);
-    red[bl][el] = acc;
+    T a0 = T(0), a1 = T(0), a2 = T(0), a3 = T(0);
+    int b = bl;
+    for (; b + 24 < rows; b += 32) {  // four independent loads in flight
+        a0 += __ldg(part + (int64_t)b * 64 * SMALLC_K + e);
+        a1 += __ldg(part + (int64_t)(b + 8) * 64 * SMALLC_K + e);
+        a2 += __ldg(part + (int64_t)(b + 16) * 64 * SMALLC_K + e);
+        a3 += __ldg(part + (int64_t)(b + 24) * 64 * SMALLC_K + e);
+    }
+    for (; b < rows; b += 8) a0 += __ldg(part + (int64_t)b * 64 * SMALLC_K + e);
+    red[bl][el] = (a0 + a1) + (a2 + a3);
     __syncthreads();
     const int o = e / SMALLC_K, k = e - o * SMALLC_K;
     if (bl == 0 && o < K && k < CRS)

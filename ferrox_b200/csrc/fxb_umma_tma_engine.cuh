@@ -82,6 +82,13 @@ struct TmaConvParams {
     int64_t img_stride, nstr, goff[TMA_MAX_CLS], gys, gxs;
     int n_img, Hv, Wv;  // valid images and patch-grid extent
     int vec_store;      // 1: four consecutive rows are four consecutive, 16-byte aligned output floats (selects the VEC kernel)
+    // split-K (forward convolutions with fewer tiles than SMs; ncls == 1): split z of a tile contracts the
+    // stages [z * stages_per_split, ...) and writes raw partial sums to out + z * split_stride; bias and
+    // activation are applied by the kernel that adds the splits
+    int splits = 1, stages_per_split = 0;
+    int64_t split_stride = 0;
+    // stages of K accumulated in TMEM before the drain warps add the accumulator into their f32 registers
+    int drain_group = 1;
 };
 
 enum : int { TMA_WAIT_STAGE_EMPTY = 11, TMA_WAIT_STAGE_FULL = 12, TMA_WAIT_ACC_FULL = 13, TMA_WAIT_DRAIN = 14,
@@ -111,20 +118,26 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int total_items = prm.tm * prm.tn * prm.ncls;
+    const int total_items = prm.tm * prm.tn * prm.ncls * prm.splits;
     const bool three_pass = prm.three_pass != 0;
     // item t -> (stride class, patch tile, column tile); the K length depends on the class
     // The classes have different K lengths; rotating the class with the round of the persistent loop gives
     // every CTA a mix of them (without it CTA b would always draw class b % ncls when the grid is a multiple
     // of ncls).  The rotation is constant inside a group of ncls consecutive items, so the map stays one to one.
     const int rot_ok = (gridDim.x % prm.ncls) == 0;
-    auto decode = [&](int t, int& cls, int& mt, int& nt) -> int {
+    auto decode = [&](int t, int& cls, int& mt, int& nt, int& z, int& s_begin) -> int {
         const int round = rot_ok ? t / (int)gridDim.x : 0;
         cls = (t + round) % prm.ncls;
         const int rest = t / prm.ncls;
         mt = rest % prm.tm;
-        nt = rest / prm.tm;
-        return (prm.kchunks[cls] + TMA_KCH - 1) / TMA_KCH;
+        const int ntz = rest / prm.tm;
+        nt = ntz % prm.tn;
+        z = ntz / prm.tn;
+        const int all = (prm.kchunks[cls] + TMA_KCH - 1) / TMA_KCH;
+        if (prm.splits == 1) { s_begin = 0; return all; }
+        s_begin = z * prm.stages_per_split;
+        const int e = min(all, s_begin + prm.stages_per_split);
+        return e > s_begin ? e - s_begin : 0;
     };
     const int TW = 1 << prm.tw_log, TH = 1 << prm.th_log;
 
@@ -179,8 +192,8 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
         uint32_t pit = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-            int cls, mt, nt;
-            const int nstages = decode(t, cls, mt, nt);
+            int cls, mt, nt, z, s_begin;
+            const int nstages = decode(t, cls, mt, nt, z, s_begin);
             uint32_t g, pr, py, px;
             prm.dPP.divmod((uint32_t)mt, g, pr);
             prm.dPW.divmod(pr, py, px);
@@ -202,7 +215,7 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                 if (has_copy) {
                     if (is_a) {
                         const int j = lane & 7;
-                        const int kc = sb * TMA_KCH + j;
+                        const int kc = (s_begin + sb) * TMA_KCH + j;
                         uint32_t tap, q, jr, js;
                         prm.dQ.divmod((uint32_t)kc, tap, q);
                         prm.dS[cls].divmod(tap, jr, js);
@@ -223,7 +236,7 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                                     y, n_base, plane);
                     } else {
                         tma_load_3d(is_lo ? b_lo : b_hi, is_lo ? &prm.b_lo[cls] : &prm.b_hi[cls], bar, 0, nt * (BN / 16),
-                                    sb * TMA_KCH);
+                                    (s_begin + sb) * TMA_KCH);
                     }
                 }
                 ++pit;
@@ -241,13 +254,15 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc<BN>();
-            uint32_t mit = 0;  // stages consumed = main-accumulator groups issued
+            uint32_t sit = 0;  // stages consumed
+            uint32_t mit = 0;  // main-accumulator groups issued
             uint32_t tix = 0;
+            const int G = prm.drain_group;
             bool ok = true;
             bool issued_any = false;
             for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-                int cls, mt, nt;
-                const int nstages = decode(t, cls, mt, nt);
+                int cls, mt, nt, z, s_begin;
+                const int nstages = decode(t, cls, mt, nt, z, s_begin);
                 if (nstages == 0) continue;
                 const uint32_t cb = tix % Cfg::NCORR;
                 if (three_pass) {
@@ -256,15 +271,18 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                     if (!ok) break;
                 }
                 const uint32_t d_corr = tmem_base + cb * BN;
+                int in_group = 0;
                 for (int sb = 0; sb < nstages; ++sb) {
-                    const int s = (int)(mit % Cfg::STAGES);
-                    const uint32_t ph = (mit / Cfg::STAGES) & 1u;
+                    const int s = (int)(sit % Cfg::STAGES);
+                    const uint32_t ph = (sit / Cfg::STAGES) & 1u;
                     const int b = (int)(mit % Cfg::NBUF);
                     ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_flag, status, TMA_WAIT_STAGE_FULL);
                     if (!ok) break;
-                    ok = mbar_wait_bounded(smem_u32(&acce_bar[b]), ((mit / Cfg::NBUF) & 1u) ^ 1u, abort_flag, status,
-                                           TMA_WAIT_ACC_EMPTY);
-                    if (!ok) break;
+                    if (in_group == 0) {
+                        ok = mbar_wait_bounded(smem_u32(&acce_bar[b]), ((mit / Cfg::NBUF) & 1u) ^ 1u, abort_flag, status,
+                                               TMA_WAIT_ACC_EMPTY);
+                        if (!ok) break;
+                    }
                     tc_fence_after_sync();
                     const uint32_t a_hi = smem_u32(stage_base + (size_t)s * Cfg::STAGE_BYTES);
                     const uint32_t a_lo = a_hi + Cfg::A_BYTES;
@@ -282,12 +300,16 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                             umma_tf32(d_corr, dal, dbh, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
                             umma_tf32(d_corr, dah, dbl, idesc, 1u);
                         }
-                        umma_tf32(d_main, dah, dbh, idesc, kk == 0 ? 0u : 1u);
+                        umma_tf32(d_main, dah, dbh, idesc, (kk == 0 && in_group == 0) ? 0u : 1u);
                     }
                     issued_any = true;
                     umma_commit(smem_u32(&empty_bar[s]));
-                    umma_commit(smem_u32(&accf_bar[b]));
-                    ++mit;
+                    ++sit;
+                    if (++in_group == G || sb == nstages - 1) {
+                        umma_commit(smem_u32(&accf_bar[b]));
+                        ++mit;
+                        in_group = 0;
+                    }
                 }
                 if (!ok) break;
                 if (three_pass) umma_commit(smem_u32(&corrf_bar[cb]));
@@ -316,12 +338,13 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
         uint32_t git = 0, tix = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
-            int cls, mt, nt;
-            const int nstages = decode(t, cls, mt, nt);
+            int cls, mt, nt, z, s_begin;
+            const int nstages = decode(t, cls, mt, nt, z, s_begin);
             float acc[DCOLS];
 #pragma unroll
             for (int i = 0; i < DCOLS; ++i) acc[i] = 0.f;
-            for (int g = 0; g < nstages && ok; ++g) {
+            const int ngroups = (nstages + prm.drain_group - 1) / prm.drain_group;
+            for (int g = 0; g < ngroups && ok; ++g) {
                 const int b = (int)(git % Cfg::NBUF);
                 ok = mbar_wait_bounded(smem_u32(&accf_bar[b]), (git / Cfg::NBUF) & 1u, abort_flag, status, TMA_WAIT_ACC_FULL);
                 ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-wide
@@ -377,7 +400,9 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
             const int ty = (ml >> prm.tw_log) & (TH - 1), tx = ml & (TW - 1);
             const int img = (int)g * prm.ni + ni, oy = (int)py * TH + ty, ox = (int)px * TW + tx;
             const bool row_ok = img < prm.n_img && oy < prm.Hv && ox < prm.Wv;
-            const int64_t moff = (int64_t)img * prm.img_stride + prm.goff[cls] + (int64_t)oy * prm.gys + (int64_t)ox * prm.gxs;
+            const int64_t moff = (int64_t)img * prm.img_stride + prm.goff[cls] + (int64_t)oy * prm.gys + (int64_t)ox * prm.gxs +
+                                 (int64_t)z * prm.split_stride;
+            const bool final_values = prm.splits == 1;  // raw partial sums otherwise
             if (active) {
                 const int j4 = lane & 3;
                 // vector path: output offset of the first of this lane's group of four rows
@@ -385,20 +410,21 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                 const bool ok4 = __shfl_sync(0xffffffffu, row_ok ? 1 : 0, lane & ~3) != 0;
                 // bias and activation in place; identity / ReLU are two instructions per value, sigmoid and
                 // tanh take a separate pass through the out-of-line function (kept off the common path)
-                const bool relu = prm.act == FXB_ACT_RELU;
+                const bool relu = final_values && prm.act == FXB_ACT_RELU;
 #pragma unroll
                 for (int c = 0; c < DCOLS; c += 16) {
                     const int nb = nt * BN + cbeg + ((c + rot) & (DCOLS - 1));
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const int n = nb + i;
-                        const float bvi = bias_in_smem ? bias_s[n < TMA_BIAS_MAX ? n : 0]
-                                                       : ((prm.bias != nullptr && n < prm.ncols) ? __ldg(prm.bias + n) : 0.f);
+                        const float bvi = !final_values ? 0.f
+                                          : bias_in_smem ? bias_s[n < TMA_BIAS_MAX ? n : 0]
+                                                         : ((prm.bias != nullptr && n < prm.ncols) ? __ldg(prm.bias + n) : 0.f);
                         const float t = acc[c + i] + bvi;
                         acc[c + i] = (relu && !(t > 0.f)) ? 0.f : t;
                     }
                 }
-                if (prm.act > FXB_ACT_RELU) {
+                if (final_values && prm.act > FXB_ACT_RELU) {
 #pragma unroll
                     for (int i = 0; i < DCOLS; ++i) acc[i] = act_apply_outlined<float>(acc[i], prm.act);
                 }

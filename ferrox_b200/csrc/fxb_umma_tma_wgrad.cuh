@@ -41,6 +41,7 @@ struct TmaWgradParams {
     int ncls;                 // stride classes (sh * sw)
     int bw, bh;               // output-pixel box of one stage, bw * bh = 8
     FastDiv dSpg, dPW;        // stage -> (image group, box row, box column)
+    int drain_group;          // stages of K accumulated in TMEM before the drain warps add them into registers
     float* out;               // dW (splits == 1) or the partial-sum workspace
     int64_t split_stride;     // elements between the partial results of consecutive splits
 };
@@ -186,7 +187,8 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
             const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(prm.Cb >> 3) << 17) |
                                    ((uint32_t)(UMMA_BM >> 4) << 24);
             const uint32_t lbo_b = (uint32_t)prm.Cb * 16u;
-            uint32_t mit = 0, tix = 0;
+            uint32_t sit = 0, mit = 0, tix = 0;  // stages consumed, accumulator groups issued, tiles
+            const int G = prm.drain_group;
             bool ok = true;
             bool issued_any = false;
             for (int t = blockIdx.x; t < total_items && ok; t += gridDim.x) {
@@ -200,15 +202,18 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
                     if (!ok) break;
                 }
                 const uint32_t d_corr = tmem_base + cb * BN;
+                int in_group = 0;
                 for (int sb = 0; sb < nst; ++sb) {
-                    const int s = (int)(mit % Cfg::STAGES);
-                    const uint32_t ph = (mit / Cfg::STAGES) & 1u;
+                    const int s = (int)(sit % Cfg::STAGES);
+                    const uint32_t ph = (sit / Cfg::STAGES) & 1u;
                     const int b = (int)(mit % Cfg::NBUF);
                     ok = mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_flag, status, TMA_WAIT_STAGE_FULL);
                     if (!ok) break;
-                    ok = mbar_wait_bounded(smem_u32(&acce_bar[b]), ((mit / Cfg::NBUF) & 1u) ^ 1u, abort_flag, status,
-                                           TMA_WAIT_ACC_EMPTY);
-                    if (!ok) break;
+                    if (in_group == 0) {
+                        ok = mbar_wait_bounded(smem_u32(&acce_bar[b]), ((mit / Cfg::NBUF) & 1u) ^ 1u, abort_flag, status,
+                                               TMA_WAIT_ACC_EMPTY);
+                        if (!ok) break;
+                    }
                     tc_fence_after_sync();
                     const uint32_t a_hi = smem_u32(stage_base + (size_t)s * Cfg::STAGE_BYTES);
                     const uint32_t a_lo = a_hi + Cfg::A_BYTES;
@@ -229,13 +234,17 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
                                 umma_tf32(d_corr + dcol, dal, dbh, idesc, (sb > 0 || kk > 0) ? 1u : 0u);
                                 umma_tf32(d_corr + dcol, dah, dbl, idesc, 1u);
                             }
-                            umma_tf32(d_main + dcol, dah, dbh, idesc, kk == 0 ? 0u : 1u);
+                            umma_tf32(d_main + dcol, dah, dbh, idesc, (kk == 0 && in_group == 0) ? 0u : 1u);
                         }
                     }
                     issued_any = true;
                     umma_commit(smem_u32(&empty_bar[s]));
-                    umma_commit(smem_u32(&accf_bar[b]));
-                    ++mit;
+                    ++sit;
+                    if (++in_group == G || sb == nst - 1) {
+                        umma_commit(smem_u32(&accf_bar[b]));
+                        ++mit;
+                        in_group = 0;
+                    }
                 }
                 if (!ok) break;
                 if (three_pass) umma_commit(smem_u32(&corrf_bar[cb]));
@@ -264,7 +273,8 @@ umma_tma_wgrad_kernel(const __grid_constant__ TmaWgradParams prm, DeviceStatus* 
             float acc[DCOLS];
 #pragma unroll
             for (int i = 0; i < DCOLS; ++i) acc[i] = 0.f;
-            for (int g = 0; g < nst && ok; ++g) {
+            const int ngroups = (nst + prm.drain_group - 1) / prm.drain_group;
+            for (int g = 0; g < ngroups && ok; ++g) {
                 const int b = (int)(git % Cfg::NBUF);
                 ok = mbar_wait_bounded(smem_u32(&accf_bar[b]), (git / Cfg::NBUF) & 1u, abort_flag, status, TMA_WAIT_ACC_FULL);
                 ok = __all_sync(0xffffffffu, ok);

@@ -109,6 +109,10 @@ class CudaOps:
         self._use_workspace = code != 1
         self._check(self.lib.fxb_set_operand_path(self.h, code))
 
+    def set_accumulate_stages(self, stages: int):
+        """K stages (of 32) the f32 convolution kernels accumulate in TMEM between two drains: 1, 2 or 4."""
+        self._check(self.lib.fxb_set_accumulate_stages(self.h, int(stages)))
+
     def set_math_mode(self, mode):
         self._check(self.lib.fxb_set_math_mode(self.h, mode))
 

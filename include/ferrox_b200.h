@@ -74,6 +74,11 @@ int fxb_set_math_mode(fxb_handle_t h, int mode);
 #define FXB_PATH_GATHER 1
 #define FXB_PATH_CP_ASYNC 2
 int fxb_set_operand_path(fxb_handle_t h, int path);
+/* The tensor-map f32 convolution kernels keep a running sum in TMEM for `stages` K stages of 32 values (1, 2 or 4)
+ * before the drain warps add it into their f32 registers with round-to-nearest adds.  The tensor core's own
+ * accumulation truncates, so fewer drains trade a little accuracy (still far inside the f32 tolerance) for fewer
+ * TMEM reads. */
+int fxb_set_accumulate_stages(fxb_handle_t h, int stages);
 /* 0 (default) reproduces the reference's Sigmoid::gradient, dY*s*(s-1)
  * (src/ops/unary.rs:270-273); 1 selects the derivative dY*s*(1-s). */
 int fxb_set_sigmoid_grad_mode(fxb_handle_t h, int math_mode);
