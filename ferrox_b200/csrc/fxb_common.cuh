@@ -29,7 +29,7 @@ struct Context {
     int math_mode = FXB_MATH_3XTF32;
     int sigmoid_grad_math = 0;  // 0 = the reference's literal s*(s-1); 1 = s*(1-s)
     int operand_path = 0;       // FXB_PATH_*: which operand paths the f32 convolutions may take
-    int drain_group = 1;        // 32-deep K stages accumulated in TMEM between two drains (fxb_set_accumulate_stages)
+    int drain_group = 4;        // 32-deep K stages accumulated in TMEM between two drains (fxb_set_accumulate_stages)
     DeviceStatus* d_status = nullptr;
     // 8 KB of handle-owned device scratch right after the status block (per-CTA partial sums of the
     // loss kernel + its arrival counter); used by one stream at a time, like the handle itself.

@@ -77,7 +77,8 @@ int fxb_set_operand_path(fxb_handle_t h, int path);
 /* The tensor-map f32 convolution kernels keep a running sum in TMEM for `stages` K stages of 32 values (1, 2 or 4)
  * before the drain warps add it into their f32 registers with round-to-nearest adds.  The tensor core's own
  * accumulation truncates, so fewer drains trade a little accuracy (still far inside the f32 tolerance) for fewer
- * TMEM reads. */
+ * TMEM reads.  Default 4 (measured on conv 64->128 at batch 1024: kernel 13 % faster than with 1, maximum error
+ * against an f64 evaluation 3e-6 instead of 2e-6 at an output rms of 1.4). */
 int fxb_set_accumulate_stages(fxb_handle_t h, int stages);
 /* 0 (default) reproduces the reference's Sigmoid::gradient, dY*s*(s-1)
  * (src/ops/unary.rs:270-273); 1 selects the derivative dY*s*(1-s). */
