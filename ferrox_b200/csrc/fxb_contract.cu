@@ -862,10 +862,21 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         return fail(c, FXB_ERR_UNSUPPORTED, "this convolution has no separate operand pre-pass");
     }
     if (c->operand_path == FXB_PATH_AUTO && g.CRS <= SMALLC_K && (size_t)g.K * SMALLC_K * sizeof(T) <= 48 * 1024) {
-        // a handful of input values per output: one thread per output pixel on the CUDA cores
+        // a handful of input values per output: two output pixels per thread on the CUDA cores
         const int64_t npix = (int64_t)g.N * g.P;
-        smallc_conv_fwd_kernel<T><<<(unsigned)((npix + 255) / 256), 256, (size_t)g.K * SMALLC_K * sizeof(T), st>>>(X, W, bias, Y, g,
-                                                                                                           npix, act);
+        const unsigned blocks = (unsigned)((npix + 511) / 512);
+        const int kp = (g.CRS + 3) / 4 * 4;
+        const size_t smem = (size_t)g.K * kp * sizeof(T);
+        switch (kp) {
+            case 4: smallc_conv_fwd2_kernel<T, 4><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 8: smallc_conv_fwd2_kernel<T, 8><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 12: smallc_conv_fwd2_kernel<T, 12><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 16: smallc_conv_fwd2_kernel<T, 16><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 20: smallc_conv_fwd2_kernel<T, 20><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 24: smallc_conv_fwd2_kernel<T, 24><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            case 28: smallc_conv_fwd2_kernel<T, 28><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+            default: smallc_conv_fwd2_kernel<T, 32><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
+        }
         return launch_status(c, "smallc_conv_fwd_kernel");
     }
     if constexpr (sizeof(T) == 4) {
@@ -1318,8 +1329,12 @@ static int conv_wgrad_impl(Context* c, const T* X, const T* dY, const T* Yact, T
         if (ws != nullptr && ws_bytes >= smallc_wgrad_bytes(c, npix, sizeof(T))) {
             T* part = static_cast<T*>(ws);
             T* dbpart = db ? part + (size_t)blocks * 64 * SMALLC_K : nullptr;
-            smallc_conv_wgrad_kernel<T><<<blocks, 256, 0, st>>>(X, dY, act == FXB_ACT_NONE ? nullptr : Yact, part, dbpart, g, npix,
-                                                                act, c->sigmoid_grad_math);
+            if constexpr (sizeof(T) == 4)
+                smallc_conv_wgrad_f32_kernel<<<blocks, 256, 0, st>>>(X, dY, act == FXB_ACT_NONE ? nullptr : Yact, part, dbpart, g, npix,
+                                                                     act, c->sigmoid_grad_math);
+            else
+                smallc_conv_wgrad_kernel<T><<<blocks, 256, 0, st>>>(X, dY, act == FXB_ACT_NONE ? nullptr : Yact, part, dbpart, g, npix,
+                                                                    act, c->sigmoid_grad_math);
             rc = launch_status(c, "smallc_conv_wgrad_kernel");
             if (rc) return rc;
             smallc_wgrad_finish_kernel<T><<<64 * SMALLC_K / 32, 256, 0, st>>>(part, dW, g.K, g.CRS, blocks);

@@ -181,6 +181,64 @@ __global__ void __launch_bounds__(256) smallc_conv_fwd_kernel(const T* __restric
     }
 }
 
+// The same forward pass with two output pixels per thread and the im2col row trimmed to KP = CRS rounded up to
+// a multiple of four: every filter value read from shared memory feeds two pixels, the padded columns beyond KP
+// are not multiplied, and four independent FMA chains run per output channel.
+template <typename T, int KP>
+__global__ void __launch_bounds__(256) smallc_conv_fwd2_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                               const T* __restrict__ bias, T* __restrict__ y, ConvGeom g,
+                                                               int64_t npix, int act) {
+    extern __shared__ __align__(16) unsigned char smallc_smem[];
+    __shared__ SmallcTap taps[SMALLC_K];
+    T* ws = reinterpret_cast<T*>(smallc_smem);  // [K][KP], zero padded
+    for (int e = threadIdx.x; e < g.K * KP; e += blockDim.x) {
+        const int o = e / KP, k = e - o * KP;
+        ws[e] = k < g.CRS ? __ldg(w + (int64_t)o * g.CRS + k) : T(0);
+    }
+    if (threadIdx.x < SMALLC_K) taps[threadIdx.x] = smallc_tap(g, threadIdx.x);
+    __syncthreads();
+    // pixels t and t + 256 of this block's 512 (flattened (n, oy, ox) order): both stay coalesced across the warp
+    const int64_t pix0 = (int64_t)blockIdx.x * 512 + threadIdx.x;
+    if (pix0 >= npix) return;
+    T v[2][KP];
+    T* yo[2];
+    bool live[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+        const int64_t pix = pix0 + 256 * q;
+        live[q] = pix < npix;
+        uint32_t n = 0, p = 0, oy = 0, ox = 0;
+        if (live[q]) {
+            g.dP.divmod((uint32_t)pix, n, p);
+            g.dOW.divmod(p, oy, ox);
+        }
+        const int y0 = (int)oy * g.sh - g.ph, x0 = (int)ox * g.sw - g.pw;
+        const T* xn = x + (int64_t)n * g.C * g.HW + (int64_t)y0 * g.W + x0;
+#pragma unroll
+        for (int k = 0; k < KP; ++k) {
+            const SmallcTap t = taps[k];
+            const bool in = live[q] && t.valid && (unsigned)(y0 + t.r) < (unsigned)g.H && (unsigned)(x0 + t.s) < (unsigned)g.W;
+            v[q][k] = in ? __ldg(xn + t.off) : T(0);
+        }
+        yo[q] = y + (int64_t)n * g.K * g.P + p;
+    }
+    for (int o = 0; o < g.K; ++o) {
+        const T* wr = ws + o * KP;
+        T a0 = T(0), a1 = T(0), b0 = T(0), b1 = T(0);
+#pragma unroll
+        for (int k = 0; k < KP; k += 2) {
+            const T w0 = wr[k], w1 = wr[k + 1];
+            a0 += w0 * v[0][k];
+            a1 += w1 * v[0][k + 1];
+            b0 += w0 * v[1][k];
+            b1 += w1 * v[1][k + 1];
+        }
+        const T bv = bias ? __ldg(bias + o) : T(0);
+        if (live[0]) yo[0][(int64_t)o * g.P] = act_apply<T>((a0 + a1) + bv, act);
+        if (live[1]) yo[1][(int64_t)o * g.P] = act_apply<T>((b0 + b1) + bv, act);
+    }
+}
+
 // Filter gradient, K <= 64: block = 256 threads = 64 output channels x 4 groups of 8 im2col columns.
 // Each block walks over tiles of 32 output pixels (grid-stride), staging dZ[32][64] and the im2col rows
 // [32][32] in shared memory, and writes its partial sums part[block][o][32] and dbpart[block][o].
@@ -262,6 +320,120 @@ __global__ void __launch_bounds__(256) smallc_conv_wgrad_kernel(const T* __restr
 #pragma unroll
     for (int j = 0; j < 8; ++j) pr[j] = acc[j];
     if (kg == 0 && dbpart != nullptr) dbpart[(int64_t)blockIdx.x * 64 + o] = dbs;
+}
+
+// The same filter gradient for f32 with a 4 x 8 register tile per thread: block = 4 pixel sub-streams x
+// (16 groups of 4 output channels x 4 groups of 8 im2col columns).  Per pixel a thread reads its four dZ values
+// and eight im2col values with three 16-byte shared-memory loads and issues 32 FMAs, so the kernel is bound by
+// the FMA pipe instead of by shared-memory bandwidth.  Same partial-sum layout as the generic kernel
+// (part[block][64][32], dbpart[block][64]); the four sub-streams are added in order at the end.
+__global__ void __launch_bounds__(256) smallc_conv_wgrad_f32_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                                    const float* __restrict__ yact, float* __restrict__ part,
+                                                                    float* __restrict__ dbpart, ConvGeom g, int64_t npix, int act,
+                                                                    int sig_math) {
+    // dz_s [32][68] and in_s [32][32] during the main loop; the sub-stream partials [4][64][33] at the end
+    __shared__ __align__(16) float smem_f[4 * 64 * 33];
+    float (*dz_s)[68] = reinterpret_cast<float (*)[68]>(smem_f);
+    float (*in_s)[SMALLC_K] = reinterpret_cast<float (*)[SMALLC_K]>(smem_f + 32 * 68);
+    const int sub = threadIdx.x >> 6, w64 = threadIdx.x & 63;
+    const int og = w64 & 15, kg = w64 >> 4;
+    float acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[a][j] = 0.f;
+    float dbs[4] = {0.f, 0.f, 0.f, 0.f};
+    const int64_t ntiles = (npix + 31) / 32;
+    // staging roles: dZ values (pixel tid&31, channels 8*(tid>>5) .. +7); im2col values (pixel (tid>>5) + 8j, column tid&31)
+    const int lane_e = threadIdx.x & 31, row_e = threadIdx.x >> 5;
+    const SmallcTap tap = smallc_tap(g, lane_e);
+    float rdy[8], rya[8], rx[4];
+    auto fetch = [&](int64_t tile) {
+        const int64_t pix0 = tile * 32;
+        const int64_t pix = pix0 + lane_e;
+        const bool pin = pix < npix;
+        uint32_t n = 0, p = 0;
+        if (pin) g.dP.divmod((uint32_t)pix, n, p);
+        const int64_t base = (int64_t)n * g.K * g.P + p;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int oc = row_e * 8 + j;
+            rdy[j] = 0.f;
+            rya[j] = 0.f;
+            if (pin && oc < g.K) {
+                const int64_t src = base + (int64_t)oc * g.P;
+                rdy[j] = __ldg(dy + src);
+                if (yact) rya[j] = __ldg(yact + src);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t pixj = pix0 + row_e + 8 * j;
+            float v = 0.f;
+            if (tap.valid && pixj < npix) {
+                uint32_t n2, p2, oy, ox;
+                g.dP.divmod((uint32_t)pixj, n2, p2);
+                g.dOW.divmod(p2, oy, ox);
+                const int y0 = (int)oy * g.sh - g.ph, x0 = (int)ox * g.sw - g.pw;
+                if ((unsigned)(y0 + tap.r) < (unsigned)g.H && (unsigned)(x0 + tap.s) < (unsigned)g.W)
+                    v = __ldg(x + (int64_t)n2 * g.C * g.HW + (int64_t)y0 * g.W + x0 + tap.off);
+            }
+            rx[j] = v;
+        }
+    };
+    if ((int64_t)blockIdx.x < ntiles) fetch(blockIdx.x);
+    for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            v[j] = rdy[j];
+            if (yact) v[j] *= act_grad_factor<float>(rya[j], act, sig_math);
+        }
+        *reinterpret_cast<float4*>(&dz_s[lane_e][row_e * 8]) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(&dz_s[lane_e][row_e * 8 + 4]) = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) in_s[row_e + 8 * j][lane_e] = rx[j];
+        __syncthreads();
+        if (tile + gridDim.x < ntiles) fetch(tile + gridDim.x);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int px = sub * 8 + q;
+            const float4 d = *reinterpret_cast<const float4*>(&dz_s[px][og * 4]);
+            const float4 c0 = *reinterpret_cast<const float4*>(&in_s[px][kg * 8]);
+            const float4 c1 = *reinterpret_cast<const float4*>(&in_s[px][kg * 8 + 4]);
+            const float dd[4] = {d.x, d.y, d.z, d.w};
+            const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                if (kg == 0) dbs[a] += dd[a];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[a][j] += dd[a] * cc[j];
+            }
+        }
+        __syncthreads();
+    }
+    // add the four pixel sub-streams in order
+    float (*red)[64][33] = reinterpret_cast<float (*)[64][33]>(smem_f);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) red[sub][og * 4 + a][kg * 8 + j] = acc[a][j];
+    __syncthreads();
+    for (int e = threadIdx.x; e < 64 * SMALLC_K; e += 256) {
+        const int o = e >> 5, k = e & 31;
+        part[((int64_t)blockIdx.x * 64 + o) * SMALLC_K + k] = (red[0][o][k] + red[1][o][k]) + (red[2][o][k] + red[3][o][k]);
+    }
+    if (dbpart != nullptr) {
+        __syncthreads();
+        if (kg == 0) {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) red[sub][og * 4 + a][0] = dbs[a];
+        }
+        __syncthreads();
+        if (threadIdx.x < 64)
+            dbpart[(int64_t)blockIdx.x * 64 + threadIdx.x] =
+                (red[0][threadIdx.x][0] + red[1][threadIdx.x][0]) + (red[2][threadIdx.x][0] + red[3][threadIdx.x][0]);
+    }
 }
 
 // dW[o][k] = sum over blocks of part[b][o][k] (k < CRS), eight interleaved running sums combined as a fixed tree.
