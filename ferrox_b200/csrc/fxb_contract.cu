@@ -249,20 +249,17 @@ __global__ void __launch_bounds__(256) pack_dz_kernel(const float* __restrict__ 
 
 // X NCHW -> XN[cls][g][iy][ix][c][4] (hi and lo): in padded coordinates (yp, xp) = (y + ph, x + pw), class
 // cls = (yp % sh) * sw + xp % sw, cell (iy, ix) = (yp / sh, xp / sw); the four values are images 4g..4g+3,
-// `Cp` channels per cell (zeros beyond C, outside the image and beyond N).  With `slab_hi` the same pass also
-// writes the forward kernel's class slabs S[cls * Q + c/4][n][iy][ix][4] (one read of X for both).
+// `Cp` channels per cell (zeros beyond C, outside the image and beyond N).
 // Block = 4 images x 64 channels x a band of RY padded rows, walked in chunks of 32 cells through shared
 // memory: reads coalesced along x; writes ordered by destination address (the cells of a chunk sorted by
 // class, 64 channels = 1 KB per cell), so that a block emits runs of many KB instead of scattered pieces.
 constexpr int XN_CT = 64;  // channels per block
-__global__ void __launch_bounds__(256) pack_xn_kernel(const float* __restrict__ x, float* __restrict__ xn_hi,
-                                                      float* __restrict__ xn_lo, float* __restrict__ slab_hi,
-                                                      float* __restrict__ slab_lo, int N, int C, int Cp, int Q, int H, int W,
-                                                      int ph, int pw, int Hc, int Wc, int N4, int RY, FastDiv dWp, FastDiv dsh,
+__global__ void __launch_bounds__(256, 4) pack_xn_kernel(const float* __restrict__ x, float* __restrict__ xn_hi,
+                                                      float* __restrict__ xn_lo, int N, int C, int Cp, int H, int W, int ph,
+                                                      int pw, int Hc, int Wc, int N4, int RY, FastDiv dWp, FastDiv dsh,
                                                       FastDiv dsw) {
     __shared__ float t[4][XN_CT][33];
     __shared__ long long cell_off[32];   // XN float offset of the cell's channel 0, in destination order; -1 = no cell
-    __shared__ long long cell_slab[32];  // slab offset (in cells) of the cell in plane cls * Q of image 0; -1 = no cell
     __shared__ int cell_src[32];         // which cell of the chunk that is
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int c0 = blockIdx.x * XN_CT, g = blockIdx.z;
@@ -306,33 +303,15 @@ __global__ void __launch_bounds__(256) pack_xn_kernel(const float* __restrict__ 
             }
             cell_src[pos] = lane;
             cell_off[pos] = e < cells ? ((((long long)cls * N4 + g) * Hc + iy) * Wc + ix) * Cp * 4 : -1;
-            cell_slab[pos] = e < cells ? ((long long)cls * Q * N * Hc + iy) * Wc + ix : -1;
         }
         __syncthreads();
-        if (xn_hi != nullptr) {
-            for (int i = threadIdx.x; i < 32 * XN_CT; i += 256) {
-                const int pos = i / XN_CT, cl = i - pos * XN_CT;
-                const long long off = cell_off[pos];
-                const int c = c0 + cl;
-                if (off >= 0 && c < Cp) {
-                    const int el = cell_src[pos];
-                    store_split4(xn_hi, xn_lo, off + (long long)c * 4, t[0][cl][el], t[1][cl][el], t[2][cl][el], t[3][cl][el]);
-                }
-            }
-        }
-        if (slab_hi != nullptr) {
-            // lanes = the cells in destination order (consecutive cells of a class are 16 bytes apart in a plane)
-            const long long plane_cells = (long long)Hc * Wc;
-            for (int i = threadIdx.x; i < 32 * XN_CT; i += 256) {
-                const int pos = i & 31, rest = i >> 5;
-                const int n4 = rest & 3, ql = rest >> 2;
-                const int n = 4 * g + n4, qq = (c0 >> 2) + ql;
-                const long long cb = cell_slab[pos];
-                if (cb >= 0 && n < N && qq < Q) {
-                    const int el = cell_src[pos];
-                    store_split4(slab_hi, slab_lo, (cb + ((long long)qq * N + n) * plane_cells) * 4, t[n4][4 * ql][el],
-                                 t[n4][4 * ql + 1][el], t[n4][4 * ql + 2][el], t[n4][4 * ql + 3][el]);
-                }
+        for (int i = threadIdx.x; i < 32 * XN_CT; i += 256) {
+            const int pos = i / XN_CT, cl = i - pos * XN_CT;
+            const long long off = cell_off[pos];
+            const int c = c0 + cl;
+            if (off >= 0 && c < Cp) {
+                const int el = cell_src[pos];
+                store_split4(xn_hi, xn_lo, off + (long long)c * 4, t[0][cl][el], t[1][cl][el], t[2][cl][el], t[3][cl][el]);
             }
         }
         __syncthreads();
@@ -776,7 +755,7 @@ static void set_vec_store(TmaConvParams& prm) {
 // phase: which part of the call runs (FPROP_ALL, or one half for timing the two separately).
 enum : int { FPROP_ALL = 0, FPROP_PREPASS_ONLY = 1, FPROP_MAIN_ONLY = 2 };
 static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo, const ConvGeom& g, int Cp, int Hc, int Wc,
-                          cudaStream_t st, float* slab_hi, float* slab_lo, int Q);
+                          cudaStream_t st);
 // xn_hi / xn_lo (optional): the operand pre-pass also leaves the filter-gradient kernel's packed input
 // (xn_cp channels per cell) there, for a backward pass that follows.
 static int conv_fprop_tma(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
@@ -794,18 +773,17 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     if (!encode_filter_maps(prm, w.b_hi, w.b_lo, l.rows_pad, g.RS * l.Q, bn)) return FXB_OK;
     *used = true;
     if (phase != FPROP_MAIN_ONLY) {
-        int rc;
-        if (xn_hi != nullptr) {  // one pass over X writes the class slabs and the packed input of the filter gradient
-            rc = launch_pack_xn(c, X, xn_hi, xn_lo, g, xn_cp, l.Hc, l.Wc, st, w.a_hi, w.a_lo, l.Q);
-        } else {
-            const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
-            const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
-            split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
-                                                                      total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
-                                                                      FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
-            rc = launch_status(c, "split_image_to_class_slabs_kernel");
-        }
+        const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
+        const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
+        split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
+                                                                  total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
+                                                                  FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
+        int rc = launch_status(c, "split_image_to_class_slabs_kernel");
         if (rc) return rc;
+        if (xn_hi != nullptr) {  // (a single pass writing both layouts measured slower than the two passes)
+            rc = launch_pack_xn(c, X, xn_hi, xn_lo, g, xn_cp, l.Hc, l.Wc, st);
+            if (rc) return rc;
+        }
         FilterClassBase fc{};
         const int ftotal = g.RS * l.Q * l.rows_pad;
         const int fblocks = std::max(1, std::min((ftotal + 255) / 256, c->sm_count * 8));
@@ -884,21 +862,10 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         return fail(c, FXB_ERR_UNSUPPORTED, "this convolution has no separate operand pre-pass");
     }
     if (c->operand_path == FXB_PATH_AUTO && g.CRS <= SMALLC_K && (size_t)g.K * SMALLC_K * sizeof(T) <= 48 * 1024) {
-        // a handful of input values per output: two output pixels per thread on the CUDA cores
+        // a handful of input values per output: one thread per output pixel on the CUDA cores
         const int64_t npix = (int64_t)g.N * g.P;
-        const unsigned blocks = (unsigned)((npix + 511) / 512);
-        const int kp = (g.CRS + 3) / 4 * 4;
-        const size_t smem = (size_t)g.K * kp * sizeof(T);
-        switch (kp) {
-            case 4: smallc_conv_fwd2_kernel<T, 4><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 8: smallc_conv_fwd2_kernel<T, 8><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 12: smallc_conv_fwd2_kernel<T, 12><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 16: smallc_conv_fwd2_kernel<T, 16><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 20: smallc_conv_fwd2_kernel<T, 20><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 24: smallc_conv_fwd2_kernel<T, 24><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            case 28: smallc_conv_fwd2_kernel<T, 28><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-            default: smallc_conv_fwd2_kernel<T, 32><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act); break;
-        }
+        smallc_conv_fwd_kernel<T><<<(unsigned)((npix + 255) / 256), 256, (size_t)g.K * SMALLC_K * sizeof(T), st>>>(X, W, bias, Y, g,
+                                                                                                           npix, act);
         return launch_status(c, "smallc_conv_fwd_kernel");
     }
     if constexpr (sizeof(T) == 4) {
@@ -1204,17 +1171,21 @@ static TmaWgradLayout tma_wgrad_layout(const Context* c, const ConvGeom& g) {
     return l;
 }
 
-// x -> XN, the packed input of the filter-gradient kernel (and, with slab pointers, the forward kernel's class
-// slabs of Q channel groups in the same pass).
+// x -> XN, the packed input of the filter-gradient kernel.
 static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo, const ConvGeom& g, int Cp, int Hc, int Wc,
-                          cudaStream_t st, float* slab_hi = nullptr, float* slab_lo = nullptr, int Q = 0) {
+                          cudaStream_t st) {
     const int n4 = (g.N + 3) / 4;
     const int Wp = Wc * g.sw, Hp = Hc * g.sh;
     const int ry = std::max(1, std::min(Hp, (256 + Wp - 1) / Wp));  // about eight 32-cell chunks per block
     if (n4 > 65535 || (Hp + ry - 1) / ry > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Conv2D batch too large for the packed operand pass");
-    dim3 grid((std::max(Cp, Q * 4) + XN_CT - 1) / XN_CT, (Hp + ry - 1) / ry, n4);
-    pack_xn_kernel<<<grid, 256, 0, st>>>(X, xn_hi, xn_lo, slab_hi, slab_lo, g.N, g.C, Cp, Q, g.H, g.W, g.ph, g.pw, Hc, Wc, n4, ry,
-                                         FastDiv((uint32_t)Wp), FastDiv((uint32_t)g.sh), FastDiv((uint32_t)g.sw));
+    dim3 grid((Cp + XN_CT - 1) / XN_CT, (Hp + ry - 1) / ry, n4);
+    static bool carveout_set[64] = {};
+    if (!carveout_set[c->device & 63]) {  // 34 KB of static shared memory per block: ask for room for four blocks per SM
+        FXB_CUDA_OK(c, cudaFuncSetAttribute(pack_xn_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        carveout_set[c->device & 63] = true;
+    }
+    pack_xn_kernel<<<grid, 256, 0, st>>>(X, xn_hi, xn_lo, g.N, g.C, Cp, g.H, g.W, g.ph, g.pw, Hc, Wc, n4, ry, FastDiv((uint32_t)Wp),
+                                         FastDiv((uint32_t)g.sh), FastDiv((uint32_t)g.sw));
     return launch_status(c, "pack_xn_kernel");
 }
 // dY (* act'(Y)) -> DZN (+ channel slabs for the input gradient) (+ bias gradient).

@@ -181,64 +181,6 @@ __global__ void __launch_bounds__(256) smallc_conv_fwd_kernel(const T* __restric
     }
 }
 
-// The same forward pass with two output pixels per thread and the im2col row trimmed to KP = CRS rounded up to
-// a multiple of four: every filter value read from shared memory feeds two pixels, the padded columns beyond KP
-// are not multiplied, and four independent FMA chains run per output channel.
-template <typename T, int KP>
-__global__ void __launch_bounds__(256) smallc_conv_fwd2_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                               const T* __restrict__ bias, T* __restrict__ y, ConvGeom g,
-                                                               int64_t npix, int act) {
-    extern __shared__ __align__(16) unsigned char smallc_smem[];
-    __shared__ SmallcTap taps[SMALLC_K];
-    T* ws = reinterpret_cast<T*>(smallc_smem);  // [K][KP], zero padded
-    for (int e = threadIdx.x; e < g.K * KP; e += blockDim.x) {
-        const int o = e / KP, k = e - o * KP;
-        ws[e] = k < g.CRS ? __ldg(w + (int64_t)o * g.CRS + k) : T(0);
-    }
-    if (threadIdx.x < SMALLC_K) taps[threadIdx.x] = smallc_tap(g, threadIdx.x);
-    __syncthreads();
-    // pixels t and t + 256 of this block's 512 (flattened (n, oy, ox) order): both stay coalesced across the warp
-    const int64_t pix0 = (int64_t)blockIdx.x * 512 + threadIdx.x;
-    if (pix0 >= npix) return;
-    T v[2][KP];
-    T* yo[2];
-    bool live[2];
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-        const int64_t pix = pix0 + 256 * q;
-        live[q] = pix < npix;
-        uint32_t n = 0, p = 0, oy = 0, ox = 0;
-        if (live[q]) {
-            g.dP.divmod((uint32_t)pix, n, p);
-            g.dOW.divmod(p, oy, ox);
-        }
-        const int y0 = (int)oy * g.sh - g.ph, x0 = (int)ox * g.sw - g.pw;
-        const T* xn = x + (int64_t)n * g.C * g.HW + (int64_t)y0 * g.W + x0;
-#pragma unroll
-        for (int k = 0; k < KP; ++k) {
-            const SmallcTap t = taps[k];
-            const bool in = live[q] && t.valid && (unsigned)(y0 + t.r) < (unsigned)g.H && (unsigned)(x0 + t.s) < (unsigned)g.W;
-            v[q][k] = in ? __ldg(xn + t.off) : T(0);
-        }
-        yo[q] = y + (int64_t)n * g.K * g.P + p;
-    }
-    for (int o = 0; o < g.K; ++o) {
-        const T* wr = ws + o * KP;
-        T a0 = T(0), a1 = T(0), b0 = T(0), b1 = T(0);
-#pragma unroll
-        for (int k = 0; k < KP; k += 2) {
-            const T w0 = wr[k], w1 = wr[k + 1];
-            a0 += w0 * v[0][k];
-            a1 += w1 * v[0][k + 1];
-            b0 += w0 * v[1][k];
-            b1 += w1 * v[1][k + 1];
-        }
-        const T bv = bias ? __ldg(bias + o) : T(0);
-        if (live[0]) yo[0][(int64_t)o * g.P] = act_apply<T>((a0 + a1) + bv, act);
-        if (live[1]) yo[1][(int64_t)o * g.P] = act_apply<T>((b0 + b1) + bv, act);
-    }
-}
-
 // Filter gradient, K <= 64: block = 256 threads = 64 output channels x 4 groups of 8 im2col columns.
 // Each block walks over tiles of 32 output pixels (grid-stride), staging dZ[32][64] and the im2col rows
 // [32][32] in shared memory, and writes its partial sums part[block][o][32] and dbpart[block][o].

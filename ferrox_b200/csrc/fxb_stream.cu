@@ -327,9 +327,10 @@ static int pick_parts(const Context* c, const ReduceGeom& g) {
     const int64_t per_out = g.R0 * g.R1;
     int64_t units = g.K1 > 1 ? g.KB * g.K0 * ((g.K1 + 127) / 128) : g.KB * g.K0;
     if (units <= 0) units = 1;
-    // aim for >= 4 CTAs per SM, but keep every part large enough to amortise its reduction
+    // aim for >= 4 CTAs per SM (8 when the inner axis is reduced: those CTAs keep fewer bytes in flight),
+    // but keep every part large enough to amortise its reduction
     const int64_t min_len = g.K1 > 1 ? 64 : 8192;
-    int64_t parts = ((int64_t)c->sm_count * 4 + units - 1) / units;
+    int64_t parts = ((int64_t)c->sm_count * (g.K1 > 1 ? 4 : 8) + units - 1) / units;
     parts = std::min<int64_t>(parts, std::max<int64_t>(1, per_out / min_len));
     parts = std::max<int64_t>(1, std::min<int64_t>(parts, 1024));
     return (int)parts;
