@@ -366,6 +366,8 @@ def run_case(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(0)
     ops = CudaOps(0)
+    if args.accumulate_stages:
+        ops.set_accumulate_stages(args.accumulate_stages)
     fn, work, unit = make_case(args.case, ops, dev, args.dtype)
     fn()
     torch.cuda.synchronize()
@@ -460,10 +462,7 @@ def run_phases(args, rank, world, local_rank):
         print(json.dumps({"phases": phases, "n_gpus": world, "per_gpu_batch": local_b, "steps": steps,
                           "gpu_ms_total": sum(v["gpu_ms"] for v in phases.values()),
                           "host_ms_total": sum(v["host_ms"] for v in phases.values())}), flush=True)
-    net.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    teardown(world, tr, net)
 
 
 def run_ours(args, rank, world, local_rank):
@@ -523,7 +522,8 @@ def run_ours(args, rank, world, local_rank):
     ops.check_device_status()
     l0 = ops.launch_count()
     ms_total = timed(step_resident, args.steps)
-    launches = (ops.launch_count() - l0) // args.steps
+    # kernels of this library per step: counted at the C ABI (eager) or while the graph was captured (replay)
+    launches = tr.launches_per_step if (args.graph and tr.launches_per_step) else (ops.launch_count() - l0) // args.steps
     for _ in range(2):
         step_e2e()
     ms_e2e = timed(step_e2e, args.steps)
@@ -597,10 +597,28 @@ def run_ours(args, rank, world, local_rank):
                 line["configs"] = measure_configs(ops, dev, flush, peaks, tf32_peak, f64_peak)
                 ops.check_device_status()
         print(json.dumps(line), flush=True)
+    teardown(world, tr, net)
+
+
+def teardown(world, tr, net):
+    """Releases the graph before the communicator; a teardown that does not finish in 30 s ends the process
+    (the result line is out by then)."""
+    import torch
+    import torch.distributed as dist
+    tr.close()
+    torch.cuda.synchronize()
     net.close()
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        def _down():
+            dist.barrier()
+            dist.destroy_process_group()
+        t = threading.Thread(target=_down, daemon=True)
+        t.start()
+        t.join(30)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if t.is_alive():
+            os._exit(0)
 
 
 def main():
@@ -614,7 +632,10 @@ def main():
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--phases", action="store_true", help="print the per-phase timeline of the train step")
     ap.add_argument("--no-configs", action="store_true", help="skip the single-layer / microbenchmark configurations")
-    ap.add_argument("--graph", action="store_true", help="replay the train step from a CUDA graph (captured after three eager steps)")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="launch every kernel eagerly instead of replaying the step from a CUDA graph (captured after three eager steps)")
+    ap.add_argument("--accumulate-stages", type=int, default=None, choices=[1, 2, 4],
+                    help="--case only: K stages accumulated in TMEM between drains (library default 4)")
     ap.add_argument("--batch", type=int, default=None, help="--phases only: per-GPU batch (e.g. 128, the share of one of 8 GPUs)")
     args = ap.parse_args()
     # keep stdout to the one JSON line: NCCL writes its version banner (NCCL_DEBUG=VERSION/WARN) to stdout
@@ -635,7 +656,7 @@ def main():
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29511", os.path.abspath(__file__), "--gpus", str(args.gpus),
                "--steps", str(args.steps), "--warmup", str(args.warmup)] + (["--phases"] if args.phases else []) + \
-              (["--graph"] if args.graph else [])
+              ([] if args.graph else ["--no-graph"])
         sys.exit(subprocess.call(cmd))
     if args.phases:
         run_phases(args, rank, world, local_rank)

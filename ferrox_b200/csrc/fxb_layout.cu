@@ -70,11 +70,18 @@ template <typename T>
 __global__ void __launch_bounds__(256) materialize_transpose_kernel(const T* __restrict__ in, T* __restrict__ out, ViewGeom g,
                                                                     int jd, int J, int L, FastDiv dtj, FastDiv dtl) {
     __shared__ T tile[32][33];
+    __shared__ int64_t offs[2];
     uint32_t rest, tl, o, tj;
     dtl.divmod(blockIdx.x, rest, tl);
     dtj.divmod(rest, o, tj);
-    int64_t in_off, out_off;
-    outer_offsets(g, o, g.nd - 1, jd, in_off, out_off);
+    if (threadIdx.x == 0 && threadIdx.y == 0) {  // the outer coordinates are the same for the whole tile
+        int64_t io, oo;
+        outer_offsets(g, o, g.nd - 1, jd, io, oo);
+        offs[0] = io;
+        offs[1] = oo;
+    }
+    __syncthreads();
+    const int64_t in_off = offs[0], out_off = offs[1];
     const int64_t sl = g.istride[g.nd - 1], sjo = g.ostride[jd];
     const int j0 = (int)tj * 32, l0 = (int)tl * 32;
 #pragma unroll

@@ -475,7 +475,7 @@ template <typename T> __device__ __forceinline__ T lowest_val();
 template <> __device__ __forceinline__ float lowest_val<float>() { return -3.402823466e+38f; }
 template <> __device__ __forceinline__ double lowest_val<double>() { return -1.7976931348623157e+308; }
 
-constexpr int CE_MAX_BLOCKS = 256;
+constexpr int CE_MAX_BLOCKS = 960;  // per-CTA loss partials live in the handle's 8 KB scratch block
 
 template <typename T>
 __global__ void __launch_bounds__(256) softmax_ce_kernel(const T* __restrict__ logits, const T* __restrict__ targets,
@@ -569,22 +569,48 @@ template <> __device__ __forceinline__ float dev_sqrt<float>(float x) { return s
 template <> __device__ __forceinline__ double dev_sqrt<double>(double x) { return sqrt(x); }
 
 template <typename T>
+__device__ __forceinline__ void adam_update(T& p, T g, T& m, T& v, T lr, T b1, T b2, T omb1, T omb2, T eps, T wd, T bc1, T bc2,
+                                            T gscale) {
+    if (gscale != T(1)) g *= gscale;
+    const T mi = m * b1 + g * omb1;
+    const T vi = v * b2 + (g * g) * omb2;
+    m = mi;
+    v = vi;
+    const T den = dev_sqrt<T>(vi / bc2) + eps;
+    const T upd = ((mi / bc1) / den) * lr;
+    p = wd != T(0) ? (p - upd) - p * (wd * lr) : p - upd;
+}
+// One 16-byte vector of each array per thread step when the four arrays are 16-byte aligned, a scalar tail otherwise.
+template <typename T>
+__device__ __forceinline__ void adam_range(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m, T* __restrict__ v,
+                                           int64_t n, T lr, T b1, T b2, T eps, T wd, T bc1, T bc2, T gscale, int vec_ok) {
+    constexpr int V = VecOf<T>::N;
+    const T omb1 = T(1) - b1, omb2 = T(1) - b2;
+    const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+    int64_t done = 0;
+    if (vec_ok) {
+        const int64_t nvec = n / V;
+        for (int64_t i = tid; i < nvec; i += nth) {
+            T pv[V], gv[V], mv[V], vv[V];
+            vload<T>(p + i * V, pv);
+            vload<T>(g + i * V, gv);
+            vload<T>(m + i * V, mv);
+            vload<T>(v + i * V, vv);
+#pragma unroll
+            for (int e = 0; e < V; ++e) adam_update<T>(pv[e], gv[e], mv[e], vv[e], lr, b1, b2, omb1, omb2, eps, wd, bc1, bc2, gscale);
+            vstore<T>(p + i * V, pv);
+            vstore<T>(m + i * V, mv);
+            vstore<T>(v + i * V, vv);
+        }
+        done = nvec * V;
+    }
+    for (int64_t i = done + tid; i < n; i += nth) adam_update<T>(p[i], g[i], m[i], v[i], lr, b1, b2, omb1, omb2, eps, wd, bc1, bc2, gscale);
+}
+template <typename T>
 __global__ void __launch_bounds__(256) adam_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m,
                                                    T* __restrict__ v, int64_t n, T lr, T b1, T b2, T eps, T wd, T bc1,
-                                                   T bc2, T gscale) {
-    const T omb1 = T(1) - b1, omb2 = T(1) - b2;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        T gi = g[i];
-        if (gscale != T(1)) gi *= gscale;
-        const T mi = m[i] * b1 + gi * omb1;
-        const T vi = v[i] * b2 + (gi * gi) * omb2;
-        m[i] = mi;
-        v[i] = vi;
-        const T den = dev_sqrt<T>(vi / bc2) + eps;
-        const T upd = ((mi / bc1) / den) * lr;
-        const T pi = p[i];
-        p[i] = wd != T(0) ? (pi - upd) - pi * (wd * lr) : pi - upd;
-    }
+                                                   T bc2, T gscale, int vec_ok) {
+    adam_range<T>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, bc2, gscale, vec_ok);
 }
 
 // Adam with the step count in device memory, for a train step that is replayed from a CUDA graph
@@ -599,26 +625,18 @@ template <> __device__ __forceinline__ double dev_pow<double>(double b, double e
 template <typename T>
 __global__ void __launch_bounds__(256) adam_devcount_kernel(T* __restrict__ p, const T* __restrict__ g, T* __restrict__ m,
                                                             T* __restrict__ v, int64_t n, T lr, T b1, T b2, T eps, T wd,
-                                                            const long long* __restrict__ step_dev, T gscale) {
+                                                            const long long* __restrict__ step_dev, T gscale, int vec_ok) {
     const T t = (T)(*step_dev + 1);
     const T b1p = dev_pow<T>(b1, t), b2p = dev_pow<T>(b2, t);
     const T bc1 = T(1) - (b1p > T(1e-8) ? b1p : T(1e-8)), bc2 = T(1) - (b2p > T(1e-8) ? b2p : T(1e-8));
-    const T omb1 = T(1) - b1, omb2 = T(1) - b2;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        T gi = g[i];
-        if (gscale != T(1)) gi *= gscale;
-        const T mi = m[i] * b1 + gi * omb1;
-        const T vi = v[i] * b2 + (gi * gi) * omb2;
-        m[i] = mi;
-        v[i] = vi;
-        const T den = dev_sqrt<T>(vi / bc2) + eps;
-        const T upd = ((mi / bc1) / den) * lr;
-        const T pi = p[i];
-        p[i] = wd != T(0) ? (pi - upd) - pi * (wd * lr) : pi - upd;
-    }
+    adam_range<T>(p, g, m, v, n, lr, b1, b2, eps, wd, bc1, bc2, gscale, vec_ok);
 }
 __global__ void advance_step_kernel(long long* step_dev) { *step_dev += 1; }
 
+static int aligned16_all(const void* a, const void* b, const void* c, const void* d) {
+    return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+             reinterpret_cast<uintptr_t>(d)) & 15) == 0;
+}
 static int flat_grid(const Context* c, int64_t n) {
     return (int)std::max<int64_t>(1, std::min<int64_t>((n + 255) / 256, (int64_t)c->sm_count * 8));
 }
@@ -746,7 +764,7 @@ using namespace fxb;
         NEED_HANDLE(h);                                                                                                 \
         FXB_CHECK_ARG(CTX(h), B > 0 && C > 0, "softmax_ce: batch and class counts must be positive");                   \
         FXB_CHECK_ARG(CTX(h), logits && targets && loss_out, "softmax_ce: null buffer");                                \
-        const int ce_blocks = (int)std::min<int64_t>((B + 7) / 8, std::min<int>(CE_MAX_BLOCKS, CTX(h)->sm_count));       \
+        const int ce_blocks = (int)std::min<int64_t>((B + 7) / 8, std::min<int>(CE_MAX_BLOCKS, CTX(h)->sm_count * 4));   \
         T* ce_part = reinterpret_cast<T*>(static_cast<char*>(CTX(h)->d_scratch) + 64);                                  \
         unsigned int* ce_cnt = reinterpret_cast<unsigned int*>(CTX(h)->d_scratch);                                      \
         softmax_ce_kernel<T><<<ce_blocks, 256, 0, ST(s)>>>(logits, targets, loss_out, dlogits, B, C, grad_scale,        \
@@ -769,7 +787,7 @@ using namespace fxb;
         const T b1p = std::max((T)std::pow(b1, (T)step), (T)1e-8);                                                      \
         const T b2p = std::max((T)std::pow(b2, (T)step), (T)1e-8);                                                      \
         adam_kernel<T><<<flat_grid(CTX(h), n), 256, 0, ST(s)>>>(p, g, m, v, n, lr, b1, b2, eps, wd, T(1) - b1p,         \
-                                                               T(1) - b2p, gscale);                                     \
+                                                               T(1) - b2p, gscale, aligned16_all(p, g, m, v));          \
         return launch_status(CTX(h), "adam_step");                                                                      \
     }                                                                                                                   \
     extern "C" int fxb_adam_step_devcount_##SUF(fxb_handle_t h, T* p, const T* g, T* m, T* v, int64_t n, T lr, T b1,    \
@@ -779,7 +797,8 @@ using namespace fxb;
                       "adam_step_devcount: bad arguments");                                                             \
         if (n > 0)                                                                                                      \
             adam_devcount_kernel<T><<<flat_grid(CTX(h), n), 256, 0, ST(s)>>>(                                           \
-                p, g, m, v, n, lr, b1, b2, eps, wd, reinterpret_cast<const long long*>(step_dev), gscale);              \
+                p, g, m, v, n, lr, b1, b2, eps, wd, reinterpret_cast<const long long*>(step_dev), gscale,               \
+                aligned16_all(p, g, m, v));                                                                             \
         advance_step_kernel<<<1, 1, 0, ST(s)>>>(reinterpret_cast<long long*>(step_dev));                                \
         return launch_status(CTX(h), "adam_step_devcount", n > 0 ? 2 : 1);                                              \
     }

@@ -181,6 +181,7 @@ class Trainer:
         # into a CUDA graph and replayed from then on; the inputs are copied into fixed buffers first.
         self.use_graph, self._graph, self._eager_steps = bool(use_graph), None, 0
         self._x_static = self._t_static = None
+        self._graph_launches = None
         self.optimizer, self.lr, self.opt_kw = optimizer, lr, opt_kw
         self.world, self.pg = int(world_size), process_group
         self.step_count = 0
@@ -199,6 +200,19 @@ class Trainer:
         import torch.distributed as dist
         return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.pg, async_op=True)
 
+    def close(self):
+        """Releases the captured CUDA graph (it holds the all-reduce kernels of the process group's communicator:
+        drop it before the process group is destroyed)."""
+        if self._graph is not None:
+            torch.cuda.synchronize()
+            self._graph.reset()
+            self._graph = None
+
+    @property
+    def launches_per_step(self):
+        """Kernels of this library in one step (counted while the graph was captured; None before that)."""
+        return self._graph_launches
+
     def input_buffers(self):
         """(x, targets) buffers the captured graph reads, once it exists: a caller that fills them directly
         (e.g. with its host-to-device copy) and passes them to step() saves the device-to-device copy."""
@@ -216,8 +230,10 @@ class Trainer:
             self._x_static, self._t_static = torch.empty_like(x), torch.empty_like(targets)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            n0 = self.ops.launch_count()
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 self._step_body(self._x_static, self._t_static)
+            self._graph_launches = self.ops.launch_count() - n0  # every replay runs these kernels again
             self.step_count -= 1  # the capture recorded the step without running it
             self._graph = graph
         if x.data_ptr() != self._x_static.data_ptr():
