@@ -390,7 +390,7 @@ def measure_configs(ops, dev, flush, peaks, tf32_peak, f64_peak):
     out = {"roofs": {"f32_3xtf32_tflops": tf32_peak / 3.0, "f64_tflops": f64_peak, "hbm_gbs": peaks["hbm_gbs"],
                      "note": "contraction roofs = torch.matmul measured in this run (TF32 8192^3 / 3, f64 4096^3); HBM " + peaks["source"]}}
     plan = [(f"{k}_{p}", dts) for k in ("c3a", "c3b") for p in ("fwd", "dgrad", "wgrad") for dts in (("f32", "f64"),)]
-    plan += [("mlp_step", ("f32",)), ("colsum", ("f32", "f64")), ("chansum", ("f32", "f64")), ("act_bwd_relu", ("f32", "f64")),
+    plan += [("gemm", ("f32", "f64")), ("mlp_step", ("f32",)), ("colsum", ("f32", "f64")), ("chansum", ("f32", "f64")), ("act_bwd_relu", ("f32", "f64")),
              ("act_bwd_sigmoid", ("f32", "f64")), ("act_bwd_tanh", ("f32", "f64"))]
     for name, dts in plan:
         for d in dts:
@@ -405,7 +405,7 @@ def measure_configs(ops, dev, flush, peaks, tf32_peak, f64_peak):
 
 
 # ------------------------------------------------------------------------------------------ the train-step benchmark
-def setup_training(rank, world, local_rank, use_graph=False, batch_override=None):
+def setup_training(rank, world, local_rank, use_graph=False, batch_override=None, bucket_splits=None):
     import torch
     import torch.distributed as dist
     from ferrox_b200 import build
@@ -427,7 +427,7 @@ def setup_training(rank, world, local_rank, use_graph=False, batch_override=None
     xg, tg = synthetic_batch(rng, GLOBAL_BATCH)
     net = SequentialNet(ops, layers, local_b, in_shape, torch.float32)
     net.set_params(params)
-    tr = Trainer(net, optimizer="adam", lr=1e-3, world_size=world, use_graph=use_graph)
+    tr = Trainer(net, optimizer="adam", lr=1e-3, world_size=world, use_graph=use_graph, bucket_splits=bucket_splits)
     first = 0 if batch_override else rank * local_b
     xs = np.ascontiguousarray(xg[first:first + local_b])
     ts = np.ascontiguousarray(tg[first:first + local_b])
@@ -439,7 +439,7 @@ def run_phases(args, rank, world, local_rank):
     layer's backward, each all-reduce wait, optimizer) and the host time spent issuing it, averaged over the steps."""
     import torch
     import torch.distributed as dist
-    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, batch_override=args.batch)
+    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, batch_override=args.batch, bucket_splits=args.bucket_splits)
     x_dev, t_dev = torch.from_numpy(xs).to(dev), torch.from_numpy(ts).to(dev)
     for _ in range(20):
         tr.step(x_dev, t_dev)
@@ -468,7 +468,7 @@ def run_phases(args, rank, world, local_rank):
 def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
-    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, use_graph=args.graph)
+    dev, ops, net, tr, xs, ts, local_b = setup_training(rank, world, local_rank, use_graph=args.graph, bucket_splits=args.bucket_splits)
     x_pin, t_pin = torch.from_numpy(xs).pin_memory(), torch.from_numpy(ts).pin_memory()
     x_dev, t_dev = x_pin.to(dev), t_pin.to(dev)
     x_stage, t_stage = torch.empty_like(x_dev), torch.empty_like(t_dev)
@@ -636,6 +636,8 @@ def main():
                     help="launch every kernel eagerly instead of replaying the step from a CUDA graph (captured after three eager steps)")
     ap.add_argument("--accumulate-stages", type=int, default=None, choices=[1, 2, 4],
                     help="--case only: K stages accumulated in TMEM between drains (library default 4)")
+    ap.add_argument("--bucket-splits", type=lambda v: [int(t) for t in v.split(",") if t], default=None,
+                    help="parameter layers at which an all-reduce bucket starts, e.g. 3,1 (default: the trainer's two buckets)")
     ap.add_argument("--batch", type=int, default=None, help="--phases only: per-GPU batch (e.g. 128, the share of one of 8 GPUs)")
     args = ap.parse_args()
     # keep stdout to the one JSON line: NCCL writes its version banner (NCCL_DEBUG=VERSION/WARN) to stdout

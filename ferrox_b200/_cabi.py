@@ -47,6 +47,7 @@ def _sigs(real):
         "matmul": (I, [H, _P, _P, _P, I64, I64, I64, S]),
         "gemm": (I, [H, I, I, I64, I64, I64, _P, I64, _P, I64, _P, I64, _P, I, _P, SZ, S]),
         "linear_fwd": (I, [H, _P, _P, _P, _P, I64, I64, I64, I, S]),
+        "linear_fwd_ws": (I, [H, _P, _P, _P, _P, I64, I64, I64, I, _P, SZ, S]),
         "linear_bwd": (I, [H, _P, _P, _P, _P, _P, _P, _P, I64, I64, I64, I, _P, SZ, S]),
         "conv2d_forward": (I, [H, _P, _P, _P, _DP, _P, SZ, S]),
         "conv2d_bias_act_fwd": (I, [H, _P, _P, _P, _P, _DP, I, _P, SZ, S]),
@@ -93,6 +94,7 @@ _COMMON = {
     "fxb_launch_count": (ctypes.c_uint64, [c_void_p]),
     "fxb_gemm_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
     "fxb_linear_bwd_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
+    "fxb_linear_fwd_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
     "fxb_conv2d_wgrad_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_conv2d_fprop_workspace_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_conv2d_fprop_prepass_f32": (c_int, [c_void_p, c_void_p, c_void_p, _DP, c_void_p, c_size_t, c_void_p]),

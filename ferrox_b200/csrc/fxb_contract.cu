@@ -193,6 +193,90 @@ __device__ __forceinline__ void store_split4(float* hi, float* lo, int64_t o, fl
     *reinterpret_cast<float4*>(lo + o) = make_float4(v0 - __uint_as_float(h.x), v1 - __uint_as_float(h.y),
                                                      v2 - __uint_as_float(h.z), v3 - __uint_as_float(h.w));
 }
+
+// ------------------------------------------------------------------------------------------
+// Operand passes of the tensor-map GEMM: a matrix op(X)[rows][K] -> chunk-major F[K/4][rows_pad][4]
+// (hi and lo), rows beyond `rows` and K beyond the matrix are zeros.  With `aux` (same shape and
+// leading dimension) the value is first multiplied by act'(aux).
+//
+// K contiguous in memory (op(X) = X[rows][ld]): a block moves 32 rows x 32 chunks through shared
+// memory: 16-byte loads along K, 16-byte stores along the rows.
+__global__ void __launch_bounds__(256) split_matrix_kmajor_kernel(const float* __restrict__ x, const float* __restrict__ aux,
+                                                                  int64_t ld, int rows, int K, int K4, int rows_pad,
+                                                                  float* __restrict__ hi, float* __restrict__ lo, int vec_ok,
+                                                                  int act, int sig_math) {
+    __shared__ float4 tile[32][33];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int r0 = blockIdx.x * 32, q0 = blockIdx.y * 32;
+    float4 v[4], a[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + w * 4 + i, q = q0 + lane;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        a[i] = v[i];
+        if (r < rows && q < K4) {
+            const int64_t o = (int64_t)r * ld + (int64_t)q * 4;
+            if (vec_ok && q * 4 + 3 < K) {
+                v[i] = __ldg(reinterpret_cast<const float4*>(x + o));
+                if (aux) a[i] = __ldg(reinterpret_cast<const float4*>(aux + o));
+            } else {
+                float t[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (q * 4 + j < K) {
+                        t[j] = __ldg(x + o + j);
+                        if (aux) u[j] = __ldg(aux + o + j);
+                    }
+                v[i] = make_float4(t[0], t[1], t[2], t[3]);
+                a[i] = make_float4(u[0], u[1], u[2], u[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (aux) {
+            v[i].x *= act_grad_factor<float>(a[i].x, act, sig_math);
+            v[i].y *= act_grad_factor<float>(a[i].y, act, sig_math);
+            v[i].z *= act_grad_factor<float>(a[i].z, act, sig_math);
+            v[i].w *= act_grad_factor<float>(a[i].w, act, sig_math);
+            // (values outside the matrix were loaded as zeros and stay zeros: 0 * finite factor)
+        }
+        tile[w * 4 + i][lane] = v[i];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int q = q0 + w * 4 + i, r = r0 + lane;
+        if (q < K4 && r < rows_pad) {
+            const float4 t = tile[lane][w * 4 + i];
+            store_split4(hi, lo, ((int64_t)q * rows_pad + r) * 4, t.x, t.y, t.z, t.w);
+        }
+    }
+}
+// Rows contiguous in memory (op(X)(r, k) = X[k * ld + r]): one thread per (chunk, row), loads and stores
+// coalesced along the rows.
+__global__ void __launch_bounds__(256) split_matrix_rowmajor_kernel(const float* __restrict__ x, const float* __restrict__ aux,
+                                                                    int64_t ld, int rows, int K, int rows_pad, int64_t total,
+                                                                    float* __restrict__ hi, float* __restrict__ lo, int act,
+                                                                    int sig_math) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t q = idx / rows_pad;
+        const int r = (int)(idx - q * rows_pad);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int64_t k = q * 4 + j;
+            float t = 0.f;
+            if (r < rows && k < K) {
+                t = __ldg(x + k * ld + r);
+                if (aux) t *= act_grad_factor<float>(__ldg(aux + k * ld + r), act, sig_math);
+            }
+            v[j] = t;
+        }
+        store_split4(hi, lo, idx * 4, v[0], v[1], v[2], v[3]);
+    }
+}
+
 __global__ void __launch_bounds__(256) pack_dz_kernel(const float* __restrict__ dy, const float* __restrict__ yact,
                                                       float* __restrict__ dzn_hi, float* __restrict__ dzn_lo,
                                                       float* __restrict__ slab_hi, float* __restrict__ slab_lo,
@@ -540,6 +624,13 @@ static OutputWriter<T> make_plane_writer(T* out, int plane, int64_t img_stride, 
 
 static bool fits_i32(int64_t v) { return v >= 0 && v < (int64_t)1 << 31; }
 
+// GEMM on the tensor-map convolution engine (defined with that engine's host code below).
+static bool tma_gemm_wanted(const Context* c, int64_t M, int64_t N, int64_t K);
+static size_t tma_gemm_bytes(int64_t M, int64_t N, int64_t K);
+static int gemm_tma(Context* c, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+                    int64_t ldb, float* C, int64_t ldc, const float* bias, int act, const float* a_aux, int a_act, void* ws,
+                    cudaStream_t st, bool* used);
+
 template <typename T>
 static int gemm_impl(Context* c, int ta, int tb, int64_t M, int64_t N, int64_t K, const T* A, int64_t lda, const T* B,
                      int64_t ldb, T* C, int64_t ldc, const T* bias, int act, const T* a_aux, int a_act, T* rowsum_a,
@@ -550,6 +641,15 @@ static int gemm_impl(Context* c, int ta, int tb, int64_t M, int64_t N, int64_t K
     FXB_CHECK_ARG(c, A && B && C, "Matrix multiplication got a null buffer");
     FXB_CHECK_ARG(c, lda >= (ta ? M : K) && ldb >= (tb ? K : N) && ldc >= N, "Leading dimension smaller than the row length");
     FXB_CHECK_ARG(c, act >= FXB_ACT_NONE && act <= FXB_ACT_TANH, "Unknown activation code");
+    if constexpr (sizeof(T) == 4) {
+        // Large products with a workspace: operands pre-split once, tiles fed by the copy engine.
+        if (c->operand_path == FXB_PATH_AUTO && rowsum_a == nullptr && ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 &&
+            tma_gemm_wanted(c, M, N, K) && ws_bytes >= tma_gemm_bytes(M, N, K)) {
+            bool used = false;
+            const int rc = gemm_tma(c, ta, tb, M, N, K, A, lda, B, ldb, C, ldc, bias, act, a_aux, a_act, ws, st, &used);
+            if (rc || used) return rc;
+        }
+    }
     Problem<T> p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.rowsum_a = rowsum_a;
@@ -817,6 +917,92 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     const int blocks = (int)std::min<int64_t>((n + 255) / 256, (int64_t)c->sm_count * 8);
     splitk_bias_act_kernel<<<blocks, 256, 0, st>>>(prm.out, Y, n, n, fs.splits, bias, FastDiv((uint32_t)g.P), g.K, act);
     return launch_status(c, "splitk_bias_act_kernel");
+}
+
+// ---- GEMM on the same engine: C[M,N] = act(op(A) . op(B) + bias) is the forward pass of a 1x1 convolution
+// over M images of one pixel: the row operand is the slab tensor S[K/4][M][4], the column operand a
+// chunk-major "filter" F[K/4][N][4]; both come from one split pass per operand, which also absorbs
+// the transposes.  Tiles are walked in groups of 16 row tiles so that the CTAs running side by side
+// share operand rows in L2.
+static bool tma_gemm_wanted(const Context* c, int64_t M, int64_t N, int64_t K) {
+    if (M < 128 || N < 64 || K < 128 || tensor_map_encoder() == nullptr) return false;
+    const int64_t K4 = (K + 3) / 4;
+    if (!fits_i32(K4 * 4) || !fits_i32(M + 128) || !fits_i32(N + 128)) return false;
+    const int bn = tile_cols((int)std::min<int64_t>(N, 128));
+    const int64_t tiles = ((M + 127) / 128) * ((N + bn - 1) / bn);
+    return tiles >= c->sm_count / 2 && tiles < ((int64_t)1 << 30);
+}
+static size_t tma_gemm_bytes(int64_t M, int64_t N, int64_t K) {
+    const int64_t K4 = (K + 3) / 4;
+    const int bn = tile_cols((int)std::min<int64_t>(N, 128));
+    const int64_t rows_pad = (N + bn - 1) / bn * bn;
+    return carve_split_ws(nullptr, K4 * ((M + 15) / 16 * 16) * 4, K4 * rows_pad * 4).bytes;
+}
+static int launch_split_matrix(Context* c, const float* x, const float* aux, int64_t ld, bool rows_contiguous, int rows, int K,
+                               int rows_pad, float* hi, float* lo, int act, cudaStream_t st) {
+    const int K4 = (K + 3) / 4;
+    if (rows_contiguous) {
+        const int64_t total = (int64_t)K4 * rows_pad;
+        const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
+        split_matrix_rowmajor_kernel<<<blocks, 256, 0, st>>>(x, aux, ld, rows, K, rows_pad, total, hi, lo, aux ? act : FXB_ACT_NONE,
+                                                             c->sigmoid_grad_math);
+        return launch_status(c, "split_matrix_rowmajor_kernel");
+    }
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (aux == nullptr || (reinterpret_cast<uintptr_t>(aux) & 15) == 0) &&
+                        ld % 4 == 0;
+    const int gy = (K4 + 31) / 32;
+    if (gy > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Matrix multiplication: K above 8 million is not supported on this path");
+    dim3 grid((unsigned)((rows_pad + 31) / 32), (unsigned)gy);
+    split_matrix_kmajor_kernel<<<grid, 256, 0, st>>>(x, aux, ld, rows, K, K4, rows_pad, hi, lo, vec_ok ? 1 : 0,
+                                                     aux ? act : FXB_ACT_NONE, c->sigmoid_grad_math);
+    return launch_status(c, "split_matrix_kmajor_kernel");
+}
+static int gemm_tma(Context* c, int ta, int tb, int64_t M, int64_t N, int64_t K, const float* A, int64_t lda, const float* B,
+                    int64_t ldb, float* C, int64_t ldc, const float* bias, int act, const float* a_aux, int a_act, void* ws,
+                    cudaStream_t st, bool* used) {
+    *used = false;
+    const int K4 = (int)((K + 3) / 4);
+    const int bn = tile_cols((int)std::min<int64_t>(N, 128));
+    const int rows_pad = round_up((int)N, bn);
+    const int Mp = round_up((int)M, 16);
+    const SplitWs w = carve_split_ws(ws, (int64_t)K4 * Mp * 4, (int64_t)K4 * rows_pad * 4);
+    TmaConvParams prm;
+    {
+        // row operand: 16 rows x 4 floats form the innermost 256 bytes (long copy lines): dims [64, 1, Mp/16, K/4];
+        // one box = 8 row groups x 8 chunks = the 128 x 32 stage
+        const uint64_t dims[4] = {64, 1, (uint64_t)Mp / 16, (uint64_t)K4};
+        const uint64_t str[3] = {256, 256, (uint64_t)Mp * 16};
+        const uint32_t box[4] = {64, 1, 8, (uint32_t)TMA_KCH};
+        if (!encode_f32_map(&prm.a_hi, w.a_hi, 4, dims, str, box) || !encode_f32_map(&prm.a_lo, w.a_lo, 4, dims, str, box))
+            return FXB_OK;
+        prm.a_chunks = TMA_KCH;
+        prm.a_nshift = 4;
+    }
+    if (!encode_filter_maps(prm, w.b_hi, w.b_lo, rows_pad, K4, bn)) return FXB_OK;
+    *used = true;
+    // op(A)(m, k): trans_a == 0 -> A[m * lda + k] (K contiguous); trans_a == 1 -> A[k * lda + m].
+    int rc = launch_split_matrix(c, A, a_aux, lda, ta != 0, (int)M, (int)K, Mp, w.a_hi, w.a_lo, a_act, st);
+    if (rc) return rc;
+    // op(B)(k, n): trans_b == 0 -> B[k * ldb + n] (columns contiguous); trans_b == 1 -> B[n * ldb + k].
+    rc = launch_split_matrix(c, B, nullptr, ldb, tb == 0, (int)N, (int)K, rows_pad, w.b_hi, w.b_lo, FXB_ACT_NONE, st);
+    if (rc) return rc;
+    PatchPlan pp;
+    pp.tw_log = 0; pp.th_log = 0; pp.ni = 128; pp.PW = 1; pp.PH = 1;
+    set_patch(prm, pp, (int)M, 1, 1);
+    prm.tn = ((int)N + bn - 1) / bn;
+    prm.ncols = (int)N;
+    prm.ncls = 1;
+    prm.kchunks[0] = K4;
+    prm.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
+    prm.drain_group = c->drain_group;
+    prm.dQ.init((uint32_t)K4); prm.dS[0].init(1);
+    prm.Q = K4; prm.sh = 1; prm.sw = 1; prm.dir = 1; prm.by[0] = 0; prm.bx[0] = 0; prm.planes = K4;
+    prm.out = C; prm.bias = bias; prm.act = act;
+    prm.img_stride = ldc; prm.nstr = 1; prm.goff[0] = 0; prm.gys = 0; prm.gxs = 0;
+    prm.vec_store = 0;
+    prm.row_vec = (ldc % 4 == 0 && N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+    prm.group_m = 16;
+    return launch_tma(c, prm, bn, st);
 }
 
 static int conv_fprop_async(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
@@ -1470,7 +1656,7 @@ static size_t skinny_bwd_bytes(const Context* c, int64_t B, int64_t in, int64_t 
 
 template <typename T>
 static int linear_fwd_impl(Context* c, const T* X, const T* W, const T* bias, T* Y, int64_t B, int64_t in, int64_t out,
-                           int act, cudaStream_t st) {
+                           int act, cudaStream_t st, void* ws = nullptr, size_t ws_bytes = 0) {
     FXB_CHECK_ARG(c, B >= 0 && in > 0 && out > 0, "Linear layer sizes must be positive");
     if (out <= SKINNY_MAXO && fits_i32(B) && fits_i32(in)) {
         // a few output features: one warp per batch row on the CUDA cores (memory-bound)
@@ -1480,7 +1666,10 @@ static int linear_fwd_impl(Context* c, const T* X, const T* W, const T* bias, T*
         skinny_linear_fwd_kernel<T><<<(unsigned)B, 256, 0, st>>>(X, W, bias, Y, (int)B, (int)in, (int)out, act);
         return launch_status(c, "skinny_linear_fwd_kernel");
     }
-    return gemm_impl<T>(c, 0, 1, B, out, in, X, in, W, in, Y, out, bias, act, nullptr, 0, nullptr, nullptr, 0, st);
+    // (the workspace only serves the tensor-map path: this product never splits K)
+    const bool tma = sizeof(T) == 4 && ws != nullptr && tma_gemm_wanted(c, B, out, in) && ws_bytes >= tma_gemm_bytes(B, out, in);
+    return gemm_impl<T>(c, 0, 1, B, out, in, X, in, W, in, Y, out, bias, act, nullptr, 0, nullptr, tma ? ws : nullptr,
+                        tma ? ws_bytes : 0, st);
 }
 
 template <typename T>
@@ -1523,7 +1712,13 @@ static int linear_bwd_impl(Context* c, const T* X, const T* W, const T* Y, const
     int rc = gemm_impl<T>(c, 1, 0, out, in, B, dY, out, X, in, dW, in, nullptr, FXB_ACT_NONE, aux, act, db, ws, ws_bytes, st);
     if (rc) return rc;
     // dX[B,in] = dZ . W   (A(m=b,k=o) = dZ[b,o], B(n=i,k=o) = W[o,i])
-    if (dX) rc = gemm_impl<T>(c, 0, 0, B, in, out, dY, out, W, in, dX, in, nullptr, FXB_ACT_NONE, aux, act, nullptr, nullptr, 0, st);
+    //   (the workspace is free again: the dW call's kernels precede this one on the stream; without the tensor-map
+    //    path this product never splits K, as before)
+    if (dX) {
+        const bool tma = sizeof(T) == 4 && tma_gemm_wanted(c, B, in, out) && ws_bytes >= tma_gemm_bytes(B, in, out);
+        rc = gemm_impl<T>(c, 0, 0, B, in, out, dY, out, W, in, dX, in, nullptr, FXB_ACT_NONE, aux, act, nullptr, tma ? ws : nullptr,
+                          tma ? ws_bytes : 0, st);
+    }
     return rc;
 }
 
@@ -1553,6 +1748,11 @@ using namespace fxb;
                                         int64_t in, int64_t out, int act, fxb_stream_t s) {                             \
         NEED_HANDLE(h);                                                                                                 \
         return linear_fwd_impl<T>(CTX(h), X, W, bias, Y, B, in, out, act, ST(s));                                       \
+    }                                                                                                                   \
+    extern "C" int fxb_linear_fwd_ws_##SUF(fxb_handle_t h, const T* X, const T* W, const T* bias, T* Y, int64_t B,      \
+                                           int64_t in, int64_t out, int act, void* ws, size_t wsb, fxb_stream_t s) {    \
+        NEED_HANDLE(h);                                                                                                 \
+        return linear_fwd_impl<T>(CTX(h), X, W, bias, Y, B, in, out, act, ST(s), ws, wsb);                              \
     }                                                                                                                   \
     extern "C" int fxb_linear_bwd_##SUF(fxb_handle_t h, const T* X, const T* W, const T* Y, const T* dY, T* dX, T* dW,  \
                                         T* db, int64_t B, int64_t in, int64_t out, int act, void* ws, size_t wsb,       \
@@ -1633,11 +1833,21 @@ extern "C" size_t fxb_conv2d_backward_workspace_bytes(fxb_handle_t h, const fxb_
 
 extern "C" size_t fxb_gemm_workspace_bytes(fxb_handle_t h, int64_t M, int64_t N, int64_t K, size_t elem) {
     if (!h || M <= 0 || N <= 0 || K <= 0) return 0;
-    return split_ws_upper(CTX(h), M, N, K, M * N, 0, 0, elem);
+    size_t need = split_ws_upper(CTX(h), M, N, K, M * N, 0, 0, elem);
+    if (elem == 4 && tma_gemm_wanted(CTX(h), M, N, K)) need = std::max(need, tma_gemm_bytes(M, N, K));
+    return need;
+}
+extern "C" size_t fxb_linear_fwd_workspace_bytes(fxb_handle_t h, int64_t B, int64_t in, int64_t out, size_t elem) {
+    if (!h || B <= 0 || in <= 0 || out <= 0) return 0;
+    return (elem == 4 && out > SKINNY_MAXO && tma_gemm_wanted(CTX(h), B, out, in)) ? tma_gemm_bytes(B, out, in) : 0;
 }
 extern "C" size_t fxb_linear_bwd_workspace_bytes(fxb_handle_t h, int64_t B, int64_t in, int64_t out, size_t elem) {
     if (!h || B <= 0 || in <= 0 || out <= 0) return 0;
     size_t need = split_ws_upper(CTX(h), out, in, B, out * in, (int)out, 0, elem);
+    if (elem == 4 && out > SKINNY_MAXO) {
+        if (tma_gemm_wanted(CTX(h), out, in, B)) need = std::max(need, tma_gemm_bytes(out, in, B));
+        if (tma_gemm_wanted(CTX(h), B, in, out)) need = std::max(need, tma_gemm_bytes(B, in, out));
+    }
     if (out <= SKINNY_MAXO) need = std::max(need, elem == 8 ? skinny_bwd_bytes<double>(CTX(h), B, in, out) : skinny_bwd_bytes<float>(CTX(h), B, in, out));
     return need;
 }

@@ -49,6 +49,7 @@ static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 using namespace fxb;
 
 extern "C" size_t fxb_linear_bwd_workspace_bytes(fxb_handle_t, int64_t, int64_t, int64_t, size_t);
+extern "C" size_t fxb_linear_fwd_workspace_bytes(fxb_handle_t, int64_t, int64_t, int64_t, size_t);
 extern "C" size_t fxb_conv2d_wgrad_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_dgrad_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
@@ -96,6 +97,7 @@ extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_
             L.out_c = layers[i].out_channels; L.out_h = 1; L.out_w = 1;
             L.w_off = n->nparams; L.b_off = L.w_off + L.out_c * cc; L.end_off = L.b_off + L.out_c;
             ws = std::max(ws, fxb_linear_bwd_workspace_bytes(h, batch, cc, L.out_c, elem_size));
+            ws = std::max(ws, fxb_linear_fwd_workspace_bytes(h, batch, cc, L.out_c, elem_size));
         } else if (L.kind == FXB_LAYER_FLATTEN) {
             L.out_c = cc * hh * ww; L.out_h = 1; L.out_w = 1;
         } else {
@@ -168,7 +170,7 @@ template <> struct Api<float> {
                         void* ws, size_t wsb, void* packed, size_t packed_bytes, int* written, fxb_stream_t st) {
         return fxb_conv2d_bias_act_fwd_packing_f32(h, x, w, b, y, d, act, ws, wsb, packed, packed_bytes, written, st);
     }
-    static constexpr auto lin_fwd = fxb_linear_fwd_f32;
+    static constexpr auto lin_fwd = fxb_linear_fwd_ws_f32;
     static constexpr auto lin_bwd = fxb_linear_bwd_f32;
     static constexpr auto conv_bwd = fxb_conv2d_backward_f32;
     static int ce(fxb_handle_t h, const void* z, const void* t, void* l, void* g, int64_t B, int64_t C, double s, fxb_stream_t st) {
@@ -181,7 +183,7 @@ template <> struct Api<double> {
         if (written) *written = 0;
         return fxb_conv2d_bias_act_fwd_f64(h, x, w, b, y, d, act, ws, wsb, st);
     }
-    static constexpr auto lin_fwd = fxb_linear_fwd_f64;
+    static constexpr auto lin_fwd = fxb_linear_fwd_ws_f64;
     static constexpr auto lin_bwd = fxb_linear_bwd_f64;
     static constexpr auto conv_bwd = fxb_conv2d_backward_f64;
     static int ce(fxb_handle_t h, const void* z, const void* t, void* l, void* g, int64_t B, int64_t C, double s, fxb_stream_t st) {
@@ -210,7 +212,7 @@ int forward_t(Net* n, const void* x, fxb_stream_t st) {
         if (L.kind == FXB_LAYER_CONV)
             rc = Api<T>::conv_fwd(h, in, W, b, outp, &L.cd, L.act, ws, n->ws_bytes, L.packed_bytes ? n->arena + L.packed_off : nullptr,
                                   L.packed_bytes, &L.packed_valid, st);
-        else rc = Api<T>::lin_fwd(h, in, W, b, outp, n->batch, L.in_c, L.out_c, L.act, st);
+        else rc = Api<T>::lin_fwd(h, in, W, b, outp, n->batch, L.in_c, L.out_c, L.act, ws, n->ws_bytes, st);
         if (rc) return rc;
     }
     return FXB_OK;

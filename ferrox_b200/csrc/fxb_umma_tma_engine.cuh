@@ -89,6 +89,12 @@ struct TmaConvParams {
     int64_t split_stride = 0;
     // stages of K accumulated in TMEM before the drain warps add the accumulator into their f32 registers
     int drain_group = 1;
+    // GEMM use (one-pixel images): each row's columns are consecutive floats -> 16-byte stores along a row
+    int row_vec = 0;
+    int a_nshift = 0;   // the image coordinate of the row-operand map counts groups of 2^a_nshift rows
+    // > 0: items walk the tiles in groups of group_m row tiles (all column tiles of a group before the next
+    // group), so that CTAs running side by side share operand rows in L2.  splits == 1, ncls == 1 only.
+    int group_m = 0;
 };
 
 enum : int { TMA_WAIT_STAGE_EMPTY = 11, TMA_WAIT_STAGE_FULL = 12, TMA_WAIT_ACC_FULL = 13, TMA_WAIT_DRAIN = 14,
@@ -129,10 +135,20 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
         const int round = rot_ok ? t / (int)gridDim.x : 0;
         cls = (t + round) % prm.ncls;
         const int rest = t / prm.ncls;
-        mt = rest % prm.tm;
-        const int ntz = rest / prm.tm;
-        nt = ntz % prm.tn;
-        z = ntz / prm.tn;
+        if (prm.group_m > 0) {
+            const int per = prm.group_m * prm.tn;
+            const int grp = rest / per, r = rest - grp * per;
+            const int first = grp * prm.group_m;
+            const int gsz = min(prm.group_m, prm.tm - first);
+            nt = r / gsz;
+            mt = first + (r - nt * gsz);
+            z = 0;
+        } else {
+            mt = rest % prm.tm;
+            const int ntz = rest / prm.tm;
+            nt = ntz % prm.tn;
+            z = ntz / prm.tn;
+        }
         const int all = (prm.kchunks[cls] + TMA_KCH - 1) / TMA_KCH;
         if (prm.splits == 1) { s_begin = 0; return all; }
         s_begin = z * prm.stages_per_split;
@@ -233,7 +249,7 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                         }
                         if (kc >= prm.kchunks[cls]) plane = prm.planes;  // K tail: zeros
                         tma_load_4d((is_lo ? a_lo : a_hi) + (uint32_t)j * Cfg::LBO_A, is_lo ? &prm.a_lo : &prm.a_hi, bar, x * 4,
-                                    y, n_base, plane);
+                                    y, n_base >> prm.a_nshift, plane);
                     } else {
                         tma_load_3d(is_lo ? b_lo : b_hi, is_lo ? &prm.b_lo[cls] : &prm.b_hi[cls], bar, 0, nt * (BN / 16),
                                     (s_begin + sb) * TMA_KCH);
@@ -453,11 +469,20 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                         }
                     } else {
                         if (row_ok) {
+                            if (prm.row_vec) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const int n = nb + i;
-                            if (n < prm.ncols) prm.out[moff + (int64_t)n * prm.nstr] = v[i];
-                        }
+                                for (int i = 0; i < 16; i += 4) {
+                                    const int n = nb + i;
+                                    if (n < prm.ncols)
+                                        *reinterpret_cast<float4*>(prm.out + moff + n) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) {
+                                    const int n = nb + i;
+                                    if (n < prm.ncols) prm.out[moff + (int64_t)n * prm.nstr] = v[i];
+                                }
+                            }
                         }
                     }
                 }

@@ -151,8 +151,15 @@ class CudaOps:
             raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT,
                                   f"Matrix multiplication shape mismatch: ({a.shape[0]}, {a.shape[1]}) @ ({b.shape[0]}, {b.shape[1]})")
         out = self._get_tensor((a.shape[0], b.shape[1]), a)
-        self._check(self._fn("matmul", a)(self.h, _ptr(a), _ptr(b), _ptr(out), a.shape[0], b.shape[1], a.shape[1],
-                                          self._stream()))
+        M, N, K = a.shape[0], b.shape[1], a.shape[1]
+        nb = self.lib.fxb_gemm_workspace_bytes(self.h, M, N, K, a.element_size()) if M * N * K >= 1 << 24 else 0
+        if nb:
+            # large products: the general entry point with a pool workspace (split-K / tensor-map engine)
+            ws, wsb = self.workspace(nb, a.device)
+            self._check(self._fn("gemm", a)(self.h, 0, 0, M, N, K, _ptr(a), K, _ptr(b), N, _ptr(out), N, None, 0, _ptr(ws),
+                                            wsb, self._stream()))
+            return out
+        self._check(self._fn("matmul", a)(self.h, _ptr(a), _ptr(b), _ptr(out), M, N, K, self._stream()))
         return out
 
     def gemm(self, a, b, trans_a=False, trans_b=False, bias=None, act=None):
@@ -481,6 +488,12 @@ class CudaOps:
             raise FerroxB200Error(_cabi.ERR_INVALID_ARGUMENT,
                                   f"Input shape {list(x.shape)} doesn't match expected last dimension {w.shape[1]}")
         out = self._get_tensor((x.shape[0], w.shape[0]), x)
+        nb = self.lib.fxb_linear_fwd_workspace_bytes(self.h, x.shape[0], x.shape[1], w.shape[0], x.element_size())
+        if nb:
+            ws, wsb = self.workspace(nb, x.device)
+            self._check(self._fn("linear_fwd_ws", x)(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), x.shape[0], x.shape[1],
+                                                     w.shape[0], act_code(act), _ptr(ws), wsb, self._stream()))
+            return out
         self._check(self._fn("linear_fwd", x)(self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), x.shape[0], x.shape[1],
                                               w.shape[0], act_code(act), self._stream()))
         return out

@@ -90,6 +90,23 @@ def plan_buckets(offsets, nparams, tail_layers=None):
     return split_layer, split_off
 
 
+def plan_bucket_list(offsets, nparams, splits=None):
+    """All-reduce buckets in issue order: [(first_layer, start, end)].  `splits` are the parameter layers at which a
+    bucket starts, e.g. [3, 1] for five layers = buckets of layers {3,4} (+ the loss slot), {1,2}, {0}; a bucket is
+    issued as soon as backward has finished its first layer.  None: the two buckets of plan_buckets."""
+    n = len(offsets)
+    if splits is None:
+        splits = [plan_buckets(offsets, nparams)[0]]
+    cuts = sorted({int(s) for s in splits if 0 < int(s) < n}, reverse=True)
+    out, end = [], nparams + 1
+    for first in cuts + [0]:
+        start = offsets[first][0]
+        if start < end:
+            out.append((first, start, end))
+            end = start
+    return out
+
+
 class SequentialNet:
     """Flat parameter / gradient buffers + activation arena bound to one fxb_net."""
 
@@ -170,12 +187,13 @@ class Trainer:
     Data parallel: every rank holds the same parameters and runs the step on its slice of the
     global batch with the loss seed scaled by 1/world, so the SUM all-reduce of the flat gradient
     buffer yields the global-batch mean gradient and every rank applies the same update.  The
-    gradients of the last `tail_layers` parameter layers (and the loss slot) are reduced while
-    the remaining layers are still in backward.
+    gradients are reduced in buckets of consecutive layers (`bucket_splits`, see plan_bucket_list; by default the
+    last `tail_layers` parameter layers and the loss slot, then the rest), each issued while the layers before it
+    are still in backward.
     """
 
     def __init__(self, net: SequentialNet, optimizer="sgd", lr=0.01, world_size=1, process_group=None, tail_layers=None,
-                 use_graph=False, **opt_kw):
+                 use_graph=False, bucket_splits=None, **opt_kw):
         self.net, self.ops = net, net.ops
         # use_graph: after three eager steps the whole step (kernels, all-reduces, optimizer) is captured once
         # into a CUDA graph and replayed from then on; the inputs are copied into fixed buffers first.
@@ -185,7 +203,9 @@ class Trainer:
         self.optimizer, self.lr, self.opt_kw = optimizer, lr, opt_kw
         self.world, self.pg = int(world_size), process_group
         self.step_count = 0
-        self.split_layer, self.split_off = plan_buckets(net.offsets, net.nparams, tail_layers)
+        if bucket_splits is None:
+            bucket_splits = [plan_buckets(net.offsets, net.nparams, tail_layers)[0]]
+        self.buckets = plan_bucket_list(net.offsets, net.nparams, bucket_splits)
         if optimizer == "adam":
             self.m = torch.zeros_like(net.params)
             self.v = torch.zeros_like(net.params)
@@ -250,15 +270,14 @@ class Trainer:
         net.forward(x)
         net.loss(targets, 1.0 / self.world)
         works = []
-        if self.world > 1 and self.split_layer > 0:
-            net.backward_range(x, n - 1, self.split_layer)
-            works.append(self._allreduce(net.grads[self.split_off:]))        # tail bucket + loss slot
-            net.backward_range(x, self.split_layer - 1, 0)
-            works.append(self._allreduce(net.grads[: self.split_off]))
+        if self.world > 1:
+            last = n - 1
+            for first, start, end in self.buckets:   # the last layers' bucket (with the loss slot) goes first
+                net.backward_range(x, last, first)
+                works.append(self._allreduce(net.grads[start:end]))
+                last = first - 1
         else:
             net.backward_range(x, n - 1, 0)
-            if self.world > 1:
-                works.append(self._allreduce(net.grads))
         for w in works:
             w.wait()
         self._optimizer_step()
@@ -300,15 +319,13 @@ class Trainer:
         mark("loss")
         net.loss(targets, 1.0 / self.world)
         works = []
+        starts = {first: (start, end) for first, start, end in self.buckets}
         for pi in range(n - 1, -1, -1):
             mark(f"backward_layer{pi}")
             net.backward_range(x, pi, pi)
-            if self.world > 1 and self.split_layer > 0 and pi == self.split_layer:
-                mark("allreduce_tail_issue")
-                works.append(self._allreduce(net.grads[self.split_off:]))
-        if self.world > 1:
-            mark("allreduce_head_issue")
-            works.append(self._allreduce(net.grads[: self.split_off] if self.split_layer > 0 else net.grads))
+            if self.world > 1 and pi in starts:
+                mark(f"allreduce_issue_from_layer{pi}")
+                works.append(self._allreduce(net.grads[starts[pi][0]:starts[pi][1]]))
         mark("allreduce_wait")
         for w in works:
             w.wait()

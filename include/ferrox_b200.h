@@ -106,7 +106,9 @@ int fxb_matmul_f64(fxb_handle_t h, const double* A, const double* B, double* C, 
 /* General form with transposed views instead of the clone+transpose+materialize of
  * MatMul::gradient (src/ops/matrix.rs:45-52; src/backend/storage/cuda.rs:826-857):
  * C[M,N] = act(op(A) . op(B) + bias[N]);  op(A) is A[M,K] (ld = lda) or, with trans_a, the
- * transpose of A[K,M].  workspace may be NULL (no split-K). */
+ * transpose of A[K,M].  workspace may be NULL (no split-K, and no tensor-map engine: with a workspace of
+ * fxb_gemm_workspace_bytes, large f32 products pre-split both operands into it (which also absorbs the
+ * transposes) and run on the kernel of the convolutions, tiles fed by the copy engine). */
 int fxb_gemm_f32(fxb_handle_t h, int trans_a, int trans_b, int64_t M, int64_t N, int64_t K, const float* A,
                  int64_t lda, const float* B, int64_t ldb, float* C, int64_t ldc, const float* bias, int act,
                  void* workspace, size_t workspace_bytes, fxb_stream_t stream);
@@ -126,6 +128,16 @@ int fxb_linear_fwd_f32(fxb_handle_t h, const float* X, const float* W, const flo
                        int64_t in_features, int64_t out_features, int act, fxb_stream_t stream);
 int fxb_linear_fwd_f64(fxb_handle_t h, const double* X, const double* W, const double* bias, double* Y, int64_t B,
                        int64_t in_features, int64_t out_features, int act, fxb_stream_t stream);
+/* The same with a workspace (fxb_linear_fwd_workspace_bytes; 0 when none is of use): large f32 layers then
+ * run on the tensor-map engine (operands pre-split into the workspace, tiles fed by the copy engine). */
+int fxb_linear_fwd_ws_f32(fxb_handle_t h, const float* X, const float* W, const float* bias, float* Y, int64_t B,
+                          int64_t in_features, int64_t out_features, int act, void* workspace, size_t workspace_bytes,
+                          fxb_stream_t stream);
+int fxb_linear_fwd_ws_f64(fxb_handle_t h, const double* X, const double* W, const double* bias, double* Y, int64_t B,
+                          int64_t in_features, int64_t out_features, int act, void* workspace, size_t workspace_bytes,
+                          fxb_stream_t stream);
+size_t fxb_linear_fwd_workspace_bytes(fxb_handle_t h, int64_t B, int64_t in_features, int64_t out_features,
+                                      size_t elem_size);
 int fxb_linear_bwd_f32(fxb_handle_t h, const float* X, const float* W, const float* Y, const float* dY, float* dX,
                        float* dW, float* db, int64_t B, int64_t in_features, int64_t out_features, int act,
                        void* workspace, size_t workspace_bytes, fxb_stream_t stream);

@@ -46,10 +46,15 @@ def _worker(rank, world, port, q):
         flat[nparams] = loss
         split_layer, split_off = plan_buckets(offs, nparams)
         assert 0 < split_layer < len(offs) and split_off == offs[split_layer][0]
+        from ferrox_b200.train import plan_bucket_list
+        assert plan_bucket_list(offs, nparams) == [(split_layer, split_off, nparams + 1), (0, 0, split_off)]
+        buckets = plan_bucket_list(offs, nparams, [3, 1])   # three buckets, last layers (+ loss slot) first
+        assert [b[0] for b in buckets] == [3, 1, 0] and buckets[0][2] == nparams + 1 and buckets[-1][1] == 0
+        assert all(buckets[i][1] == buckets[i + 1][2] for i in range(2))   # the buckets tile the buffer
         buf = torch.from_numpy(flat)
-        w1 = dist.all_reduce(buf[split_off:], async_op=True)   # tail bucket (+ loss slot) first
-        w2 = dist.all_reduce(buf[:split_off], async_op=True)
-        w1.wait(); w2.wait()
+        works = [dist.all_reduce(buf[start:end], async_op=True) for _, start, end in buckets]
+        for w in works:
+            w.wait()
         gl, gg = orc.net_forward_backward(olayers, params, x, t)
         ref = np.concatenate([np.concatenate([dw.ravel(), db.ravel()]) for dw, db in gg])
         err = np.abs(buf[:nparams].numpy() - ref).max()

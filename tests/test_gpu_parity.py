@@ -194,6 +194,65 @@ def test_matmul_and_transposed_modes(ops, oracle, dtype, M, N, K):
     assert_parity(ops.gemm(dev(A.T.copy()), dev(B.T.copy()), trans_a=True, trans_b=True), ref, "TT")
 
 
+# shapes with at least half as many 128-row tiles as the chip has SMs: f32 products with a workspace then run on
+# the tensor-map engine (two operand split passes + the convolution kernel = 3 launches)
+TMA_GEMM_SHAPES = [(1200, 1000, 520), (1187, 1021, 523), (4096, 320, 128), (9600, 64, 260)]
+
+
+@pytest.mark.parametrize("M,N,K", TMA_GEMM_SHAPES)
+def test_gemm_on_tensor_map_engine(ops, oracle, M, N, K):
+    rng = np.random.default_rng(M + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = kaiming(rng, (K, N), K, np.float32)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float32)
+    ref = oracle.matmul(A, B)
+    exact = A.astype(np.float64) @ B.astype(np.float64)
+    n0 = ops.launch_count()
+    nn = ops.matmul(dev(A), dev(B))
+    assert ops.launch_count() - n0 == 3, "the tensor-map GEMM path was not taken"
+    assert_parity(nn, ref, "NN")
+    # about as close to the exact product as the f32 CPU path
+    assert np.abs(host(nn) - exact).max() <= max(2 * np.abs(ref - exact).max(), 1e-5)
+    n0 = ops.launch_count()
+    assert_parity(ops.gemm(dev(A), dev(B.T.copy()), trans_b=True), ref, "NT")
+    assert_parity(ops.gemm(dev(A.T.copy()), dev(B), trans_a=True), ref, "TN")
+    assert_parity(ops.gemm(dev(A.T.copy()), dev(B.T.copy()), trans_a=True, trans_b=True), ref, "TT")
+    assert ops.launch_count() - n0 == 9
+    yref = oracle.act_fwd(oracle.linear_fwd(A, B.T.copy(), bias), 1)
+    assert_parity(ops.gemm(dev(A), dev(B), bias=dev(bias), act="relu"), yref, "bias + relu epilogue")
+    again = ops.matmul(dev(A), dev(B))
+    assert torch.equal(nn, again)
+
+
+@pytest.mark.parametrize("act", [0, 1, 3])
+def test_large_linear_layer_on_tensor_map_engine(ops, oracle, act):
+    B, i, o = 1280, 1024, 1280
+    rng = np.random.default_rng(17 + act)
+    X = rng.standard_normal((B, i)).astype(np.float32)
+    W = kaiming(rng, (o, i), i, np.float32)
+    b = (rng.standard_normal(o) * 0.1).astype(np.float32)
+    z = oracle.linear_fwd(X, W, b)
+    yref = oracle.act_fwd(z, act) if act else z
+    n0 = ops.launch_count()
+    y = ops.linear_forward(dev(X), dev(W), dev(b), act)
+    assert ops.launch_count() - n0 == 3, "the tensor-map GEMM path was not taken"
+    assert_parity(y, yref, "linear forward")
+    dY = (rng.standard_normal((B, o)) / B).astype(np.float32)
+    dz = oracle.act_bwd(dY, z if act == 1 else yref, act) if act else dY
+    dxr, dwr, dbr = oracle.linear_bwd(X, W, dz)
+    yt = dev(yref)
+    dx, dw, db = ops.linear_backward(dev(X), dev(W), dev(dY), yt if act else None, act)
+    assert_parity(dx, dxr, "linear dX")
+    assert_parity(dw, dwr, "linear dW")
+    assert_parity(db, dbr, "linear db")
+    # without the bias gradient the filter-side product takes the tensor-map path as well (dZ^T . X)
+    n0 = ops.launch_count()
+    dx2, dw2, _ = ops.linear_backward(dev(X), dev(W), dev(dY), yt if act else None, act, need_db=False)
+    assert ops.launch_count() - n0 == 6
+    assert_parity(dw2, dwr, "linear dW (tensor-map)")
+    assert torch.equal(dx, dx2)
+
+
 def test_matmul_unit_scale_inputs_against_exact(ops, oracle):
     """N(0,1) x N(0,1) at K=784: the CUDA f32 result must be about as close to the exact product
     as the f32 CPU path is (both are compared with an f64 evaluation)."""
