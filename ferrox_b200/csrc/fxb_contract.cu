@@ -1048,7 +1048,9 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         return fail(c, FXB_ERR_UNSUPPORTED, "this convolution has no separate operand pre-pass");
     }
     if (c->operand_path == FXB_PATH_AUTO && g.CRS <= SMALLC_K && (size_t)g.K * SMALLC_K * sizeof(T) <= 48 * 1024) {
-        // a handful of input values per output: one thread per output pixel on the CUDA cores
+        // a handful of input values per output: one thread per output pixel on the CUDA cores (the tensor-map
+        // path measured slower here: conv 3->64 on 1024 x 32 x 32 takes 0.225 ms there against 0.188 ms, its
+        // two-stage tiles are bound by the drain + epilogue of 8192 tiles)
         const int64_t npix = (int64_t)g.N * g.P;
         smallc_conv_fwd_kernel<T><<<(unsigned)((npix + 255) / 256), 256, (size_t)g.K * SMALLC_K * sizeof(T), st>>>(X, W, bias, Y, g,
                                                                                                            npix, act);
