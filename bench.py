@@ -60,7 +60,8 @@ def workload_config(world, graph=False):
     return {"launch": "CUDA graph replay" if graph else "eager launches","workload": "deep_cnn_train_step_global_batch_1024", "global_batch": GLOBAL_BATCH,
             "per_gpu_batch": GLOBAL_BATCH // world, "optimizer": "adam", "math": "3xTF32 on tcgen05, f32 accumulate",
             "parallelism": f"dp{world}", "l2": "256 MiB buffer written between timed steps (not timed)",
-            "allreduce": "NCCL sum, 2 buckets overlapped with backward" if world > 1 else "none"}
+            "allreduce": "NCCL sum, 2 buckets (last layers holding half of the parameters first), overlapped with backward"
+                         if world > 1 else "none"}
 
 
 def measured_peaks():
@@ -245,7 +246,7 @@ CASE_ALIASES = {"conv_fwd": "conv2_fwd", "conv_dgrad": "conv2_dgrad", "conv_wgra
 
 def list_cases():
     names = [f"{k}_{p}" for k in CONV_LAYERS for p in ("fwd", "dgrad", "wgrad")]
-    names += ["gemm", "mlp_step", "act_bwd_relu", "act_bwd_sigmoid", "act_bwd_tanh", "act_bwd_small", "colsum", "colsum_small",
+    names += ["gemm", "matmul_no_workspace", "mlp_step", "act_bwd_relu", "act_bwd_sigmoid", "act_bwd_tanh", "act_bwd_small", "colsum", "colsum_small",
               "chansum", "transpose", "bn_fwd", "bn_bwd", "gap_fwd", "softmax_ce", "adam", "linear_head"]
     return names + list(CASE_ALIASES)
 
@@ -278,6 +279,18 @@ def make_case(name, ops, dev, dtype_name):
         n = 4096 if dtype_name == "f32" else 2048
         A, B = randn(n, n), randn(n, n)
         return (lambda: ops.linear_forward(A, B)), 2.0 * n ** 3 / 1e12, "TFLOP/s"
+    if name == "matmul_no_workspace":
+        # fxb_matmul has no workspace argument: the first-generation engine (thread-fed operands) at the same size
+        n = 4096 if dtype_name == "f32" else 2048
+        A, B, C = randn(n, n), randn(n, n), randn(n, n)
+        fnc = ops._fn("matmul", A)
+        from ctypes import c_void_p
+        pa, pb, pc = c_void_p(A.data_ptr()), c_void_p(B.data_ptr()), c_void_p(C.data_ptr())
+
+        def call():
+            ops._check(fnc(ops.h, pa, pb, pc, n, n, n, ops._stream()))
+        call.keepalive = (A, B, C)
+        return call, 2.0 * n ** 3 / 1e12, "TFLOP/s"
     if name == "mlp_step":
         from ferrox_b200.train import SequentialNet, kaiming_uniform_params, mlp_layers
         layers, in_shape = mlp_layers()
