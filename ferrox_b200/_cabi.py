@@ -104,6 +104,10 @@ _COMMON = {
     "fxb_conv2d_packed_input_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_conv2d_bias_act_fwd_packing_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, _DP, c_int, c_void_p, c_size_t,
                                                     c_void_p, c_size_t, POINTER(c_int), c_void_p]),
+    "fxb_conv2d_bias_act_fwd_chain_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, _DP, c_int, c_void_p, c_size_t,
+                                                  c_void_p, c_size_t, POINTER(c_int), c_void_p, _DP, c_void_p, c_size_t,
+                                                  POINTER(c_int), c_void_p]),
+    "fxb_conv2d_input_slab_bytes": (c_size_t, [c_void_p, _DP, c_size_t]),
     "fxb_batch_norm_workspace_bytes": (c_size_t, [c_void_p, c_int64, c_int64, c_int64, c_size_t]),
     "fxb_sum_axes_workspace_bytes": (c_size_t, [c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_size_t]),
     "fxb_sum_axes_static_scratch_f32": (c_int, [c_void_p, c_void_p, POINTER(c_int64), c_int, POINTER(c_int), c_int, c_void_p,

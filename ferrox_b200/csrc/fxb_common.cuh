@@ -270,6 +270,35 @@ __device__ __forceinline__ uint32_t cvt_tf32_rna(float x) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
     return r;
 }
+// Four values -> their TF32 "hi" parts (round to nearest) and the exact remainders "lo", 16 bytes each.
+__device__ __forceinline__ void store_split4(float* hi, float* lo, int64_t o, float v0, float v1, float v2, float v3) {
+    uint4 h;
+    h.x = cvt_tf32_rna(v0); h.y = cvt_tf32_rna(v1); h.z = cvt_tf32_rna(v2); h.w = cvt_tf32_rna(v3);
+    *reinterpret_cast<uint4*>(hi + o) = h;
+    *reinterpret_cast<float4*>(lo + o) = make_float4(v0 - __uint_as_float(h.x), v1 - __uint_as_float(h.y),
+                                                     v2 - __uint_as_float(h.z), v3 - __uint_as_float(h.w));
+}
+
+// Where a forward kernel also leaves its output as the class slabs S[plane][n][iy][ix][4] (hi and lo) that the
+// next convolution's tensor-map kernel reads (see split_image_to_class_slabs_kernel for the layout): geometry
+// of that next layer's input.  hi == nullptr: nothing is emitted.  Only cells of real pixels are written; the
+// padding cells of the buffer must have been zeroed once.
+struct SlabEmit {
+    float* hi = nullptr;
+    float* lo = nullptr;
+    int Q = 0, sw = 1, ph = 0, pw = 0, Wc = 0;
+    FastDiv dsh, dsw;
+    int64_t plane_stride = 0;  // floats between planes: N * Hc * Wc * 4
+    int64_t img_stride = 0;    // floats between images of one plane: Hc * Wc * 4
+};
+// Offset (floats) of chunk 0 of pixel (y, x) of image n; chunk q (channels 4q..4q+3) lies q * plane_stride further.
+__device__ __forceinline__ int64_t slab_cell_offset(const SlabEmit& e, int n, int y, int x) {
+    uint32_t iy, cy, ix, cx;
+    e.dsh.divmod((uint32_t)(y + e.ph), iy, cy);
+    e.dsw.divmod((uint32_t)(x + e.pw), ix, cx);
+    return (int64_t)((int)cy * e.sw + (int)cx) * e.Q * e.plane_stride + (int64_t)n * e.img_stride +
+           ((int64_t)iy * e.Wc + ix) * 4;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

@@ -186,13 +186,6 @@ __global__ void __launch_bounds__(256) split_filter_chunk_major_kernel(const flo
 // 32 output channels and writes dbpart[g * gridDim.x + bx][o]; partial_rows_sum_kernel adds the rows in order.
 // Block = 4 images x 32 channels x 32 pixels through shared memory: reads coalesced along the pixels,
 // writes coalesced along the channels (DZN) and along the pixels (slabs).
-__device__ __forceinline__ void store_split4(float* hi, float* lo, int64_t o, float v0, float v1, float v2, float v3) {
-    uint4 h;
-    h.x = cvt_tf32_rna(v0); h.y = cvt_tf32_rna(v1); h.z = cvt_tf32_rna(v2); h.w = cvt_tf32_rna(v3);
-    *reinterpret_cast<uint4*>(hi + o) = h;
-    *reinterpret_cast<float4*>(lo + o) = make_float4(v0 - __uint_as_float(h.x), v1 - __uint_as_float(h.y),
-                                                     v2 - __uint_as_float(h.z), v3 - __uint_as_float(h.w));
-}
 
 // ------------------------------------------------------------------------------------------
 // Operand passes of the tensor-map GEMM: a matrix op(X)[rows][K] -> chunk-major F[K/4][rows_pad][4]
@@ -854,13 +847,39 @@ static void set_vec_store(TmaConvParams& prm) {
 // described by tensor maps; the caller then takes the cp.async path.
 // phase: which part of the call runs (FPROP_ALL, or one half for timing the two separately).
 enum : int { FPROP_ALL = 0, FPROP_PREPASS_ONLY = 1, FPROP_MAIN_ONLY = 2 };
+// Chaining of forward convolutions through class slabs: a layer can take its input slabs as written by the
+// layer before it (no operand pass over X) and leave its own activated output as the slabs of the next layer.
+struct FpropChain {
+    const float* in_hi = nullptr;
+    const float* in_lo = nullptr;
+    SlabEmit emit;
+    bool emitted = false;
+};
+// Bytes of the class-slab pair [hi | lo] of a layer's input; 0 when the layer does not read slabs.
+static size_t conv_input_slab_bytes(const ConvGeom& g) {
+    if (!tma_stride_ok(g) || g.CRS <= SMALLC_K || tensor_map_encoder() == nullptr) return 0;
+    const TmaFpropLayout l = tma_fprop_layout(g);
+    if (l.image_floats / 4 >= ((int64_t)1 << 31)) return 0;
+    return 2 * align_up256((size_t)l.image_floats * 4);
+}
+static SlabEmit make_slab_emit(const ConvGeom& next, void* out) {
+    const TmaFpropLayout l = tma_fprop_layout(next);
+    SlabEmit e;
+    e.hi = static_cast<float*>(out);
+    e.lo = reinterpret_cast<float*>(static_cast<char*>(out) + align_up256((size_t)l.image_floats * 4));
+    e.Q = l.Q; e.sw = next.sw; e.ph = next.ph; e.pw = next.pw; e.Wc = l.Wc;
+    e.dsh.init((uint32_t)next.sh); e.dsw.init((uint32_t)next.sw);
+    e.img_stride = (int64_t)l.Hc * l.Wc * 4;
+    e.plane_stride = (int64_t)next.N * e.img_stride;
+    return e;
+}
 static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo, const ConvGeom& g, int Cp, int Hc, int Wc,
                           cudaStream_t st);
 // xn_hi / xn_lo (optional): the operand pre-pass also leaves the filter-gradient kernel's packed input
 // (xn_cp channels per cell) there, for a backward pass that follows.
 static int conv_fprop_tma(Context* c, const float* X, const float* W, const float* bias, float* Y, const ConvGeom& g,
                           int act, void* ws, cudaStream_t st, bool* used, int phase = FPROP_ALL, float* xn_hi = nullptr,
-                          float* xn_lo = nullptr, int xn_cp = 0) {
+                          float* xn_lo = nullptr, int xn_cp = 0, FpropChain* chain = nullptr) {
     *used = false;
     if (!tma_stride_ok(g) || tensor_map_encoder() == nullptr) return FXB_OK;
     const TmaFpropLayout l = tma_fprop_layout(g);
@@ -869,17 +888,23 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
     const int bn = tile_cols(g.K);
     const PatchPlan pp = plan_patch(g.OH, g.OW);
     TmaConvParams prm;
-    if (!encode_slab_maps(prm, w.a_hi, w.a_lo, l.Wc, l.Hc, l.planes, g.N, pp, l.Q)) return FXB_OK;
+    const bool slabs_given = chain != nullptr && chain->in_hi != nullptr;
+    const float* a_hi = slabs_given ? chain->in_hi : w.a_hi;
+    const float* a_lo = slabs_given ? chain->in_lo : w.a_lo;
+    if (!encode_slab_maps(prm, a_hi, a_lo, l.Wc, l.Hc, l.planes, g.N, pp, l.Q)) return FXB_OK;
     if (!encode_filter_maps(prm, w.b_hi, w.b_lo, l.rows_pad, g.RS * l.Q, bn)) return FXB_OK;
     *used = true;
     if (phase != FPROP_MAIN_ONLY) {
-        const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
-        const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
-        split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph, g.pw,
-                                                                  total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
-                                                                  FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
-        int rc = launch_status(c, "split_image_to_class_slabs_kernel");
-        if (rc) return rc;
+        int rc = FXB_OK;
+        if (!slabs_given) {  // (otherwise the layer before this one has written them from its epilogue)
+            const int64_t total = l.image_floats / 4 / g.sw;  // one thread per cell of all x classes
+            const int blocks = (int)std::min<int64_t>((total + 255) / 256, (int64_t)c->sm_count * 16);
+            split_image_to_class_slabs_kernel<<<blocks, 256, 0, st>>>(X, w.a_hi, w.a_lo, g.C, g.H, g.W, l.Q, g.sh, g.sw, g.ph,
+                                                                      g.pw, total, FastDiv((uint32_t)l.Wc), FastDiv((uint32_t)l.Hc),
+                                                                      FastDiv((uint32_t)g.N), FastDiv((uint32_t)l.Q), g.N, l.Hc, l.Wc);
+            rc = launch_status(c, "split_image_to_class_slabs_kernel");
+            if (rc) return rc;
+        }
         if (xn_hi != nullptr) {  // (a single pass writing both layouts measured slower than the two passes)
             rc = launch_pack_xn(c, X, xn_hi, xn_lo, g, xn_cp, l.Hc, l.Wc, st);
             if (rc) return rc;
@@ -911,6 +936,10 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
         prm.out = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up256(w.bytes));
     }
     set_vec_store(prm);
+    if (chain != nullptr && chain->emit.hi != nullptr && fs.splits == 1) {
+        prm.emit = chain->emit;
+        chain->emitted = true;
+    }
     int rc = launch_tma(c, prm, bn, st);
     if (rc || fs.splits == 1) return rc;
     const int64_t n = prm.split_stride;
@@ -1029,7 +1058,7 @@ static int conv_fprop_async(Context* c, const float* X, const float* W, const fl
 
 template <typename T>
 static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T* Y, const fxb_conv2d_desc* d, int act,
-                           void* ws, size_t ws_bytes, cudaStream_t st, int phase = FPROP_ALL) {
+                           void* ws, size_t ws_bytes, cudaStream_t st, int phase = FPROP_ALL, FpropChain* chain = nullptr) {
     ConvGeom g;
     int rc = make_geom(c, d, g);
     if (rc) return rc;
@@ -1052,8 +1081,16 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
         // path measured slower here: conv 3->64 on 1024 x 32 x 32 takes 0.225 ms there against 0.188 ms, its
         // two-stage tiles are bound by the drain + epilogue of 8192 tiles)
         const int64_t npix = (int64_t)g.N * g.P;
-        smallc_conv_fwd_kernel<T><<<(unsigned)((npix + 255) / 256), 256, (size_t)g.K * SMALLC_K * sizeof(T), st>>>(X, W, bias, Y, g,
-                                                                                                           npix, act);
+        const unsigned blocks = (unsigned)((npix + 255) / 256);
+        const size_t smem = (size_t)g.K * SMALLC_K * sizeof(T);
+        if constexpr (sizeof(T) == 4) {
+            if (chain != nullptr && chain->emit.hi != nullptr) {
+                chain->emitted = true;
+                smallc_conv_fwd_kernel<T, true><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act, chain->emit);
+                return launch_status(c, "smallc_conv_fwd_kernel");
+            }
+        }
+        smallc_conv_fwd_kernel<T, false><<<blocks, 256, smem, st>>>(X, W, bias, Y, g, npix, act, SlabEmit{});
         return launch_status(c, "smallc_conv_fwd_kernel");
     }
     if constexpr (sizeof(T) == 4) {
@@ -1064,7 +1101,7 @@ static int conv_fprop_impl(Context* c, const T* X, const T* W, const T* bias, T*
             ws_bytes >= fprop_split_bytes(c, g)) {
             if (c->operand_path != FXB_PATH_CP_ASYNC) {
                 bool used = false;
-                rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used);
+                rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, FPROP_ALL, nullptr, nullptr, 0, chain);
                 if (rc || used) return rc;
             }
             return conv_fprop_async(c, X, W, bias, Y, g, act, ws, st);
@@ -1567,7 +1604,7 @@ static size_t conv_backward_bytes(const Context* c, const ConvGeom& g) {
 // plain forward).  *packed_written reports whether it did (only the tensor-map path can).
 static int conv_fprop_packing(Context* c, const float* X, const float* W, const float* bias, float* Y,
                               const fxb_conv2d_desc* d, int act, void* ws, size_t ws_bytes, void* packed, size_t packed_bytes,
-                              int* packed_written, cudaStream_t st) {
+                              int* packed_written, cudaStream_t st, FpropChain* chain = nullptr) {
     if (packed_written) *packed_written = 0;
     ConvGeom g;
     int rc = make_geom(c, d, g);
@@ -1580,14 +1617,46 @@ static int conv_fprop_packing(Context* c, const float* X, const float* W, const 
         float* xn_hi = static_cast<float*>(packed);
         float* xn_lo = reinterpret_cast<float*>(static_cast<char*>(packed) + align_up256((size_t)l.xn_floats * 4));
         bool used = false;
-        rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, FPROP_ALL, xn_hi, xn_lo, l.Cp);
+        rc = conv_fprop_tma(c, X, W, bias, Y, g, act, ws, st, &used, FPROP_ALL, xn_hi, xn_lo, l.Cp, chain);
         if (rc) return rc;
         if (used) {
             if (packed_written) *packed_written = 1;
             return FXB_OK;
         }
     }
-    return conv_fprop_impl<float>(c, X, W, bias, Y, d, act, ws, ws_bytes, st);
+    return conv_fprop_impl<float>(c, X, W, bias, Y, d, act, ws, ws_bytes, st, FPROP_ALL, chain);
+}
+
+// The chained forward: optional input slabs (written by the previous layer's call) and optional emission of the
+// next layer's slabs.  Anything that does not fit is ignored (the call then behaves like the packing forward).
+static int conv_fprop_chain(Context* c, const float* X, const float* W, const float* bias, float* Y, const fxb_conv2d_desc* d,
+                            int act, void* ws, size_t ws_bytes, void* packed, size_t packed_bytes, int* packed_written,
+                            const void* in_slabs, const fxb_conv2d_desc* next, void* out_slabs, size_t out_slab_bytes,
+                            int* out_written, cudaStream_t st) {
+    if (out_written) *out_written = 0;
+    ConvGeom g;
+    int rc = make_geom(c, d, g);
+    if (rc) return rc;
+    FpropChain ch;
+    if (in_slabs != nullptr && (reinterpret_cast<uintptr_t>(in_slabs) & 255) == 0 && conv_input_slab_bytes(g) > 0) {
+        const TmaFpropLayout l = tma_fprop_layout(g);
+        ch.in_hi = static_cast<const float*>(in_slabs);
+        ch.in_lo = reinterpret_cast<const float*>(static_cast<const char*>(in_slabs) + align_up256((size_t)l.image_floats * 4));
+    }
+    if (next != nullptr && out_slabs != nullptr) {
+        ConvGeom g2;
+        rc = make_geom(c, next, g2);
+        if (rc) return rc;
+        FXB_CHECK_ARG(c, g2.N == g.N && g2.C == g.K && g2.H == g.OH && g2.W == g.OW,
+                      "Conv2D chain: the next layer's input shape is not this layer's output shape");
+        const size_t need = conv_input_slab_bytes(g2);
+        if (need > 0 && out_slab_bytes >= need && (reinterpret_cast<uintptr_t>(out_slabs) & 255) == 0 &&
+            c->operand_path == FXB_PATH_AUTO)
+            ch.emit = make_slab_emit(g2, out_slabs);
+    }
+    rc = conv_fprop_packing(c, X, W, bias, Y, d, act, ws, ws_bytes, packed, packed_bytes, packed_written, st, &ch);
+    if (rc == FXB_OK && out_written) *out_written = ch.emitted ? 1 : 0;
+    return rc;
 }
 
 template <typename T>
@@ -1817,6 +1886,21 @@ extern "C" int fxb_conv2d_bias_act_fwd_packing_f32(fxb_handle_t h, const float* 
                                                    size_t packed_bytes, int* packed_written, fxb_stream_t s) {
     NEED_HANDLE(h);
     return conv_fprop_packing(CTX(h), X, W, bias, Y, d, act, ws, wsb, packed_input, packed_bytes, packed_written, ST(s));
+}
+extern "C" int fxb_conv2d_bias_act_fwd_chain_f32(fxb_handle_t h, const float* X, const float* W, const float* bias, float* Y,
+                                                 const fxb_conv2d_desc* d, int act, void* ws, size_t wsb, void* packed_input,
+                                                 size_t packed_bytes, int* packed_written, const void* input_slabs,
+                                                 const fxb_conv2d_desc* next, void* output_slabs, size_t output_slab_bytes,
+                                                 int* output_slabs_written, fxb_stream_t s) {
+    NEED_HANDLE(h);
+    return conv_fprop_chain(CTX(h), X, W, bias, Y, d, act, ws, wsb, packed_input, packed_bytes, packed_written, input_slabs, next,
+                            output_slabs, output_slab_bytes, output_slabs_written, ST(s));
+}
+extern "C" size_t fxb_conv2d_input_slab_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
+    if (!h || !d || elem != 4) return 0;
+    ConvGeom g;
+    if (make_geom(CTX(h), d, g) != FXB_OK) return 0;
+    return conv_input_slab_bytes(g);
 }
 extern "C" size_t fxb_conv2d_packed_input_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem) {
     if (!h || !d || elem != 4) return 0;

@@ -19,6 +19,10 @@ struct NetLayer {
     // pass and read by the backward pass of the same step
     size_t packed_off = 0, packed_bytes = 0;
     int packed_valid = 0;
+    // conv layers (f32) that follow a conv layer: this layer's input as class slabs, written by the epilogue of
+    // the layer before it (its padding cells are zeroed once, at the first forward pass after a bind)
+    size_t slab_off = 0, slab_bytes = 0;
+    int slab_valid = 0;
     int param_index = -1;
     fxb_conv2d_desc cd{};
 };
@@ -38,6 +42,7 @@ struct Net {
     char* params = nullptr;
     char* grads = nullptr;
     char* arena = nullptr;
+    bool slabs_zeroed = false;
     // backward cursor
     int cur_grad = 0;  // which ping-pong buffer holds dL/d(output of the layer about to run)
 };
@@ -55,6 +60,7 @@ extern "C" size_t fxb_conv2d_fprop_workspace_bytes(fxb_handle_t, const fxb_conv2
 extern "C" size_t fxb_conv2d_dgrad_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_backward_workspace_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 extern "C" size_t fxb_conv2d_packed_input_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
+extern "C" size_t fxb_conv2d_input_slab_bytes(fxb_handle_t, const fxb_conv2d_desc*, size_t);
 
 extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_desc* layers, int nlayers, int64_t batch,
                               int64_t in_c, int64_t in_h, int64_t in_w, fxb_net_t* out) {
@@ -88,6 +94,7 @@ extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_
             if (i > 0) {
                 ws = std::max(ws, fxb_conv2d_backward_workspace_bytes(h, &L.cd, elem_size));
                 L.packed_bytes = fxb_conv2d_packed_input_bytes(h, &L.cd, elem_size);
+                if (n->layers.back().kind == FXB_LAYER_CONV) L.slab_bytes = fxb_conv2d_input_slab_bytes(h, &L.cd, elem_size);
             }
         } else if (L.kind == FXB_LAYER_LINEAR) {
             if (hh != 1 || ww != 1 || layers[i].out_channels <= 0) {
@@ -115,6 +122,10 @@ extern "C" int fxb_net_create(fxb_handle_t h, size_t elem_size, const fxb_layer_
             if (L.packed_bytes) {
                 L.packed_off = off;
                 off += align256(L.packed_bytes);
+            }
+            if (L.slab_bytes) {
+                L.slab_off = off;
+                off += align256(L.slab_bytes);
             }
         }
         cc = L.out_c; hh = L.out_h; ww = L.out_w;
@@ -160,6 +171,7 @@ extern "C" int fxb_net_bind(fxb_net_t net, void* params, void* grads, void* aren
     if (arena_bytes < n->arena_bytes) return fail(n->ctx, FXB_ERR_WORKSPACE, "fxb_net_bind: arena smaller than fxb_net_arena_bytes");
     FXB_CHECK_ARG(n->ctx, (reinterpret_cast<uintptr_t>(arena) & 255) == 0, "fxb_net_bind: arena must be 256-byte aligned");
     n->params = static_cast<char*>(params); n->grads = static_cast<char*>(grads); n->arena = static_cast<char*>(arena);
+    n->slabs_zeroed = false;
     return FXB_OK;
 }
 
@@ -167,8 +179,10 @@ namespace {
 template <typename T> struct Api;
 template <> struct Api<float> {
     static int conv_fwd(fxb_handle_t h, const float* x, const float* w, const float* b, float* y, const fxb_conv2d_desc* d, int act,
-                        void* ws, size_t wsb, void* packed, size_t packed_bytes, int* written, fxb_stream_t st) {
-        return fxb_conv2d_bias_act_fwd_packing_f32(h, x, w, b, y, d, act, ws, wsb, packed, packed_bytes, written, st);
+                        void* ws, size_t wsb, void* packed, size_t packed_bytes, int* written, const void* in_slabs,
+                        const fxb_conv2d_desc* next, void* out_slabs, size_t out_slab_bytes, int* out_written, fxb_stream_t st) {
+        return fxb_conv2d_bias_act_fwd_chain_f32(h, x, w, b, y, d, act, ws, wsb, packed, packed_bytes, written, in_slabs, next,
+                                                 out_slabs, out_slab_bytes, out_written, st);
     }
     static constexpr auto lin_fwd = fxb_linear_fwd_ws_f32;
     static constexpr auto lin_bwd = fxb_linear_bwd_f32;
@@ -179,8 +193,10 @@ template <> struct Api<float> {
 };
 template <> struct Api<double> {
     static int conv_fwd(fxb_handle_t h, const double* x, const double* w, const double* b, double* y, const fxb_conv2d_desc* d,
-                        int act, void* ws, size_t wsb, void*, size_t, int* written, fxb_stream_t st) {
+                        int act, void* ws, size_t wsb, void*, size_t, int* written, const void*, const fxb_conv2d_desc*, void*,
+                        size_t, int* out_written, fxb_stream_t st) {
         if (written) *written = 0;
+        if (out_written) *out_written = 0;
         return fxb_conv2d_bias_act_fwd_f64(h, x, w, b, y, d, act, ws, wsb, st);
     }
     static constexpr auto lin_fwd = fxb_linear_fwd_ws_f64;
@@ -200,6 +216,11 @@ const char* layer_output(const Net* n, int li, const void* x) {
 template <typename T>
 int forward_t(Net* n, const void* x, fxb_stream_t st) {
     fxb_handle_t h = reinterpret_cast<fxb_handle_t>(n->ctx);
+    if (!n->slabs_zeroed) {
+        for (NetLayer& L : n->layers)
+            if (L.slab_bytes) FXB_CUDA_OK(n->ctx, cudaMemsetAsync(n->arena + L.slab_off, 0, L.slab_bytes, static_cast<cudaStream_t>(st)));
+        n->slabs_zeroed = true;
+    }
     for (int i = 0; i < (int)n->layers.size(); ++i) {
         NetLayer& L = n->layers[i];
         if (L.kind == FXB_LAYER_FLATTEN) continue;
@@ -209,10 +230,15 @@ int forward_t(Net* n, const void* x, fxb_stream_t st) {
         const T* b = reinterpret_cast<const T*>(n->params) + L.b_off;
         int rc;
         void* ws = n->ws_bytes ? n->arena + n->ws_off : nullptr;
-        if (L.kind == FXB_LAYER_CONV)
+        if (L.kind == FXB_LAYER_CONV) {
+            // the layer after this one, when it is a convolution that reads class slabs, gets them from this epilogue
+            NetLayer* nx = (i + 1 < (int)n->layers.size() && n->layers[i + 1].slab_bytes) ? &n->layers[i + 1] : nullptr;
+            if (nx) nx->slab_valid = 0;
             rc = Api<T>::conv_fwd(h, in, W, b, outp, &L.cd, L.act, ws, n->ws_bytes, L.packed_bytes ? n->arena + L.packed_off : nullptr,
-                                  L.packed_bytes, &L.packed_valid, st);
-        else rc = Api<T>::lin_fwd(h, in, W, b, outp, n->batch, L.in_c, L.out_c, L.act, ws, n->ws_bytes, st);
+                                  L.packed_bytes, &L.packed_valid, L.slab_valid ? n->arena + L.slab_off : nullptr,
+                                  nx ? &nx->cd : nullptr, nx ? n->arena + nx->slab_off : nullptr, nx ? nx->slab_bytes : 0,
+                                  nx ? &nx->slab_valid : nullptr, st);
+        } else rc = Api<T>::lin_fwd(h, in, W, b, outp, n->batch, L.in_c, L.out_c, L.act, ws, n->ws_bytes, st);
         if (rc) return rc;
     }
     return FXB_OK;

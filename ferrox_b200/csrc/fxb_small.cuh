@@ -141,10 +141,10 @@ __device__ __forceinline__ SmallcTap smallc_tap(const ConvGeom& g, int k) {
 
 // Y[n][o][p] = act(bias[o] + sum_k W[o][k] * im2col(p)[k]); one thread per output pixel, filter and the
 // column table in shared memory.
-template <typename T>
+template <typename T, bool EMIT>
 __global__ void __launch_bounds__(256) smallc_conv_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
                                                               const T* __restrict__ bias, T* __restrict__ y, ConvGeom g,
-                                                              int64_t npix, int act) {
+                                                              int64_t npix, int act, SlabEmit em) {
     extern __shared__ __align__(16) unsigned char smallc_smem[];
     __shared__ SmallcTap taps[SMALLC_K];
     T* ws = reinterpret_cast<T*>(smallc_smem);  // [K][SMALLC_K], zero padded
@@ -169,15 +169,41 @@ __global__ void __launch_bounds__(256) smallc_conv_fwd_kernel(const T* __restric
         v[k] = in ? __ldg(xn + t.off) : T(0);
     }
     T* yo = y + (int64_t)n * g.K * g.P + p;
-    for (int o = 0; o < g.K; ++o) {
-        const T* wr = ws + o * SMALLC_K;
-        T a0 = T(0), a1 = T(0);
+    if constexpr (!EMIT) {
+        for (int o = 0; o < g.K; ++o) {
+            const T* wr = ws + o * SMALLC_K;
+            T a0 = T(0), a1 = T(0);
 #pragma unroll
-        for (int k = 0; k < SMALLC_K; k += 2) {
-            a0 += wr[k] * v[k];
-            a1 += wr[k + 1] * v[k + 1];
+            for (int k = 0; k < SMALLC_K; k += 2) {
+                a0 += wr[k] * v[k];
+                a1 += wr[k + 1] * v[k + 1];
+            }
+            yo[(int64_t)o * g.P] = act_apply<T>((a0 + a1) + (bias ? __ldg(bias + o) : T(0)), act);
         }
-        yo[(int64_t)o * g.P] = act_apply<T>((a0 + a1) + (bias ? __ldg(bias + o) : T(0)), act);
+    } else {
+        // the same values also as the next convolution's class slabs: four consecutive channels per 16-byte chunk
+        const int64_t eoff = slab_cell_offset(em, (int)n, (int)oy, (int)ox);
+        for (int o4 = 0; o4 < g.K; o4 += 4) {
+            float r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int o = o4 + j;
+                r[j] = 0.f;
+                if (o < g.K) {
+                    const T* wr = ws + o * SMALLC_K;
+                    T a0 = T(0), a1 = T(0);
+#pragma unroll
+                    for (int k = 0; k < SMALLC_K; k += 2) {
+                        a0 += wr[k] * v[k];
+                        a1 += wr[k + 1] * v[k + 1];
+                    }
+                    const T t = act_apply<T>((a0 + a1) + (bias ? __ldg(bias + o) : T(0)), act);
+                    yo[(int64_t)o * g.P] = t;
+                    r[j] = (float)t;
+                }
+            }
+            store_split4(em.hi, em.lo, eoff + (int64_t)(o4 >> 2) * em.plane_stride, r[0], r[1], r[2], r[3]);
+        }
     }
 }
 

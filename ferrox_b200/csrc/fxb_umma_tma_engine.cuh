@@ -92,6 +92,8 @@ struct TmaConvParams {
     // GEMM use (one-pixel images): each row's columns are consecutive floats -> 16-byte stores along a row
     int row_vec = 0;
     int a_nshift = 0;   // the image coordinate of the row-operand map counts groups of 2^a_nshift rows
+    // forward convolutions (ncls == 1, splits == 1): also write the activated output as the next layer's class slabs
+    SlabEmit emit;
     // > 0: items walk the tiles in groups of group_m row tiles (all column tiles of a group before the next
     // group), so that CTAs running side by side share operand rows in L2.  splits == 1, ncls == 1 only.
     int group_m = 0;
@@ -419,6 +421,8 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
             const int64_t moff = (int64_t)img * prm.img_stride + prm.goff[cls] + (int64_t)oy * prm.gys + (int64_t)ox * prm.gxs +
                                  (int64_t)z * prm.split_stride;
             const bool final_values = prm.splits == 1;  // raw partial sums otherwise
+            const bool emit = prm.emit.hi != nullptr && final_values && row_ok;
+            const int64_t eoff = emit ? slab_cell_offset(prm.emit, img, oy, ox) : 0;
             if (active) {
                 const int j4 = lane & 3;
                 // vector path: output offset of the first of this lane's group of four rows
@@ -450,6 +454,16 @@ umma_tma_conv_kernel(const __grid_constant__ TmaConvParams prm, DeviceStatus* st
                     float v[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = acc[c + i];
+                    if (emit) {
+#pragma unroll
+                        for (int b4 = 0; b4 < 16; b4 += 4) {
+                            const int n = nb + b4;
+                            if (n < prm.ncols)  // channels beyond the last one of a partial chunk are zeros
+                                store_split4(prm.emit.hi, prm.emit.lo, eoff + (int64_t)(n >> 2) * prm.emit.plane_stride, v[b4],
+                                             n + 1 < prm.ncols ? v[b4 + 1] : 0.f, n + 2 < prm.ncols ? v[b4 + 2] : 0.f,
+                                             n + 3 < prm.ncols ? v[b4 + 3] : 0.f);
+                        }
+                    }
                     if constexpr (VEC) {
                         // 4x4 transposes inside groups of four lanes (= four consecutive output floats):
                         // afterwards lane j of a group holds the four rows of column 4b+j -> one 16-byte store.

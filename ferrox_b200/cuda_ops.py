@@ -273,6 +273,36 @@ class CudaOps:
                                                                  ctypes.byref(written), self._stream()))
         return out, (packed if written.value else None)
 
+    def conv2d_input_slabs(self, x_shape, w_shape, stride, padding, device):
+        """A zeroed buffer for the class slabs of a convolution's input (None when the layer reads none): what a
+        producing layer's conv2d_forward_chain writes and the consuming layer's reads."""
+        d = self._desc(x_shape, w_shape, stride, padding)
+        nb = self.lib.fxb_conv2d_input_slab_bytes(self.h, ctypes.byref(d), 4)
+        if nb == 0:
+            return None
+        buf = torch.zeros(nb + 256, dtype=torch.uint8, device=device)
+        return buf[(-buf.data_ptr()) % 256:]
+
+    def conv2d_forward_chain(self, x, w, stride, padding, bias=None, act=None, in_slabs=None, next_w_shape=None,
+                             next_stride=None, next_padding=None, out_slabs=None):
+        """f32 conv2d_forward for consecutive convolution layers: `in_slabs` = this layer's input slabs as written
+        by the previous layer's call; with the next layer's filter shape / stride / padding and `out_slabs`
+        (conv2d_input_slabs of that layer) the epilogue also writes the next layer's slabs.
+        Returns (y, out_slabs_written)."""
+        x, w = self._in(x), self._in(w)
+        d = self._desc(x.shape, w.shape, stride, padding)
+        oshape = self.conv_out_shape(x.shape, w.shape, stride, padding)
+        out = self._get_tensor(oshape, x)
+        nb = self.lib.fxb_conv2d_fprop_workspace_bytes(self.h, ctypes.byref(d), x.element_size())
+        ws, wsb = self.workspace(nb, x.device)
+        nd = self._desc(oshape, next_w_shape, next_stride, next_padding) if next_w_shape is not None else None
+        written = c_int(0)
+        self._check(self.lib.fxb_conv2d_bias_act_fwd_chain_f32(
+            self.h, _ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.byref(d), act_code(act), _ptr(ws), wsb, None, 0, None,
+            _ptr(in_slabs), ctypes.byref(nd) if nd is not None else None, _ptr(out_slabs),
+            0 if out_slabs is None else out_slabs.numel(), ctypes.byref(written), self._stream()))
+        return out, bool(written.value)
+
     def conv2d_backward(self, x, dy, w, stride, padding, y=None, act=None, need_dx=True, need_db=True, packed=None):
         """Conv2dOp::gradient (src/ops/batched.rs:194-217) in one call: (dX, dW, db) of the fused
         conv + bias + activation layer, with one operand pass over dY."""

@@ -240,6 +240,21 @@ int fxb_conv2d_bias_act_fwd_packing_f32(fxb_handle_t h, const float* X, const fl
                                         const fxb_conv2d_desc* d, int act, void* workspace, size_t workspace_bytes,
                                         void* packed_input, size_t packed_bytes, int* packed_written, fxb_stream_t stream);
 size_t fxb_conv2d_packed_input_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
+/* The same call for consecutive convolution layers (conv -> activation -> conv, src/nn/layers/conv2d.rs:197-213
+ * applied twice): the f32 tensor-map kernel reads its input as hi/lo "class slabs" that an operand pass over X
+ * normally writes into the workspace.  Here the producing layer writes them instead, from the registers of its
+ * epilogue: with `next` (the descriptor of the layer that consumes Y) and `output_slabs` (a buffer of
+ * fxb_conv2d_input_slab_bytes(next), 256-byte aligned, ZEROED ONCE by the caller: the cells of the padding ring
+ * are never written) the call also leaves act(conv + bias) there; *output_slabs_written tells whether it did
+ * (split-K and fallback paths do not).  The consuming layer then passes that buffer as `input_slabs` (NULL
+ * otherwise) and skips its operand pass; X must still be the tensor the slabs were made from.  Y, and every
+ * result computed from the slabs, are bit-identical to the unchained calls. */
+int fxb_conv2d_bias_act_fwd_chain_f32(fxb_handle_t h, const float* X, const float* W, const float* bias, float* Y,
+                                      const fxb_conv2d_desc* d, int act, void* workspace, size_t workspace_bytes,
+                                      void* packed_input, size_t packed_bytes, int* packed_written,
+                                      const void* input_slabs, const fxb_conv2d_desc* next, void* output_slabs,
+                                      size_t output_slab_bytes, int* output_slabs_written, fxb_stream_t stream);
+size_t fxb_conv2d_input_slab_bytes(fxb_handle_t h, const fxb_conv2d_desc* d, size_t elem_size);
 
 /* ---- activations: CudaOps::relu/sigmoid/tanh (src/backend/cuda/ops.rs:539-558, :620-628),
  *      kernels/activations.cu:10-48.  Backward replaces the mask/mul chains of

@@ -372,6 +372,47 @@ def test_conv2d_forward_dx_dw(ops, oracle, dtype, cfg, conv_path):
     assert_parity(dbf, oracle.sum_axes(dz, [3, 2, 0]), "bias grad fused")
 
 
+@pytest.mark.parametrize("act", ["relu", "sigmoid"])
+@pytest.mark.parametrize("batch", [5, 40])
+def test_conv2d_chained_forward_is_bit_identical(ops, oracle, act, batch):
+    """Consecutive convolutions: every producing layer writes the next layer's class slabs from its epilogue
+    (CUDA-core first layer, tensor-map layers after it; 18 channels = a partial last chunk; sigmoid(0) != 0 checks the
+    zero cells), the consuming layer skips its operand pass.  All outputs equal the unchained calls bit for bit,
+    the last one is also checked against the oracle."""
+    rng = np.random.default_rng(batch)
+    # C, K, stride, pad (3x3 filters); sized so that no layer splits K (a split-K layer does not emit slabs):
+    # one image copy per 4-channel chunk (batch 5) or per whole stage (batch 40, channels a multiple of 32)
+    specs = ([(3, 16, 1, 1), (16, 24, 2, 1), (24, 18, 1, 1), (18, 8, 2, 1)] if batch == 5 else
+             [(3, 32, 1, 1), (32, 64, 2, 1), (64, 18, 1, 1), (18, 8, 2, 1)])
+    x = rng.standard_normal((batch, 3, 20, 20)).astype(np.float32)
+    ws = [kaiming(rng, (k, c, 3, 3), c * 9, np.float32) for c, k, _, _ in specs]
+    bs = [(rng.standard_normal(k) * 0.1).astype(np.float32) for _, k, _, _ in specs]
+    plain, t = [], dev(x)
+    for (c, k, s, p), w, b in zip(specs, ws, bs):
+        t = ops.conv2d_forward(t, dev(w), (s, s), (p, p), dev(b), act)
+        plain.append(t)
+    ref = x
+    for (c, k, s, p), w, b in zip(specs, ws, bs):
+        ref = oracle.act_fwd(oracle.conv_bias_add(oracle.conv2d(ref, w, (s, s), (p, p)), b), 1 if act == "relu" else 2)
+    assert_parity(plain[-1], ref, "four chained layers")
+    t, slabs, shapes = dev(x), None, [x.shape]
+    for i, ((c, k, s, p), w, b) in enumerate(zip(specs, ws, bs)):
+        nxt = specs[i + 1] if i + 1 < len(specs) else None
+        oshape = ops.conv_out_shape(t.shape, w.shape, (s, s), (p, p))
+        out_slabs = ops.conv2d_input_slabs(oshape, ws[i + 1].shape, (nxt[2],) * 2, (nxt[3],) * 2, t.device) if nxt else None
+        if nxt:
+            assert out_slabs is not None
+        # a consuming layer must read the slabs, not X: give it a zeroed X
+        x_arg = t if slabs is None else torch.zeros_like(t)
+        y, written = ops.conv2d_forward_chain(x_arg, dev(w), (s, s), (p, p), dev(b), act, in_slabs=slabs,
+                                              next_w_shape=ws[i + 1].shape if nxt else None,
+                                              next_stride=(nxt[2],) * 2 if nxt else None,
+                                              next_padding=(nxt[3],) * 2 if nxt else None, out_slabs=out_slabs)
+        assert written == (nxt is not None)
+        assert torch.equal(y, plain[i]), f"layer {i}"
+        t, slabs = y, out_slabs
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("cfg", CONV_CASES)
 def test_conv2d_whole_backward_and_packing_forward(ops, oracle, dtype, cfg):
