@@ -381,6 +381,8 @@ def run_case(args):
     ops = CudaOps(0)
     if args.accumulate_stages:
         ops.set_accumulate_stages(args.accumulate_stages)
+    if args.single_pass:
+        ops.set_math_mode(1)
     fn, work, unit = make_case(args.case, ops, dev, args.dtype)
     fn()
     torch.cuda.synchronize()
@@ -647,6 +649,7 @@ def main():
     ap.add_argument("--no-configs", action="store_true", help="skip the single-layer / microbenchmark configurations")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every kernel eagerly instead of replaying the step from a CUDA graph (captured after three eager steps)")
+    ap.add_argument("--single-pass", action="store_true", help="--case only: one TF32 MMA per product instead of 3xTF32 (timing only)")
     ap.add_argument("--accumulate-stages", type=int, default=None, choices=[1, 2, 4],
                     help="--case only: K stages accumulated in TMEM between drains (library default 4)")
     ap.add_argument("--bucket-splits", type=lambda v: [int(t) for t in v.split(",") if t], default=None,

@@ -6,6 +6,7 @@
 #include "fxb_umma_tma_wgrad.cuh"
 #include "fxb_dmma_engine.cuh"
 #include "fxb_small.cuh"
+#include "fxb_small_umma.cuh"
 
 #include <algorithm>
 
@@ -1548,6 +1549,31 @@ static int conv_wgrad_impl(Context* c, const T* X, const T* dY, const T* Yact, T
         if (ws != nullptr && ws_bytes >= smallc_wgrad_bytes(c, npix, sizeof(T))) {
             T* part = static_cast<T*>(ws);
             T* dbpart = db ? part + (size_t)blocks * 64 * SMALLC_K : nullptr;
+            if constexpr (sizeof(T) == 4) {
+                // The tensor-core form: needs a free im2col column for the bias gradient and 16-byte chunks of
+                // four pixels that stay inside one output row.
+                const T* ya = act == FXB_ACT_NONE ? nullptr : Yact;
+                if (g.CRS < SMALLC_K && g.P % 4 == 0 && g.OW % 4 == 0 && aligned16(dY) && (ya == nullptr || aligned16(ya)) &&
+                    (reinterpret_cast<uintptr_t>(ws) & 15) == 0) {
+                    const int64_t ntiles = (npix + FLW_BK - 1) / FLW_BK;
+                    const int grid = (int)std::min<int64_t>(std::min<int64_t>(blocks, c->sm_count), ntiles);
+                    static bool attr_set[64] = {};
+                    if (!attr_set[c->device & 63]) {
+                        FXB_CUDA_OK(c, cudaFuncSetAttribute(firstlayer_wgrad_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                            FLW_SMEM_BYTES));
+                        attr_set[c->device & 63] = true;
+                    }
+                    firstlayer_wgrad_umma_kernel<<<grid, FLW_THREADS, FLW_SMEM_BYTES, st>>>(X, dY, ya, part, dbpart, g, npix, act,
+                                                                                           c->sigmoid_grad_math,
+                                                                                           c->math_mode == FXB_MATH_3XTF32 ? 1 : 0,
+                                                                                           c->d_status);
+                    rc = launch_status(c, "firstlayer_wgrad_umma_kernel");
+                    if (rc) return rc;
+                    smallc_wgrad_finish_kernel<T><<<64 * SMALLC_K / 32, 256, 0, st>>>(part, dW, g.K, g.CRS, grid);
+                    if (db) smallc_db_finish_kernel<T><<<2, 256, 0, st>>>(dbpart, db, g.K, grid);
+                    return launch_status(c, "smallc_wgrad_finish_kernel", db ? 2 : 1);
+                }
+            }
             if constexpr (sizeof(T) == 4)
                 smallc_conv_wgrad_f32_kernel<<<blocks, 256, 0, st>>>(X, dY, act == FXB_ACT_NONE ? nullptr : Yact, part, dbpart, g, npix,
                                                                      act, c->sigmoid_grad_math);
