@@ -1402,9 +1402,19 @@ static int launch_pack_xn(Context* c, const float* X, float* xn_hi, float* xn_lo
                           cudaStream_t st) {
     const int n4 = (g.N + 3) / 4;
     const int Wp = Wc * g.sw, Hp = Hc * g.sh;
-    const int ry = std::max(1, std::min(Hp, (256 + Wp - 1) / Wp));  // about eight 32-cell chunks per block
+    // Rows per block: the band height that minimises (waves of blocks at four blocks per SM) x (32-cell chunks per
+    // block + a fixed cost), so that the last wave is not mostly empty (at most about eight chunks per block).
+    const int gx = (Cp + XN_CT - 1) / XN_CT;
+    int ry = 1;
+    double best = 1e300;
+    for (int r = 1; r <= Hp && (r == 1 || r * Wp <= 288); ++r) {
+        const int64_t blocks = (int64_t)gx * ((Hp + r - 1) / r) * n4;
+        const int64_t waves = (blocks + (int64_t)c->sm_count * 4 - 1) / ((int64_t)c->sm_count * 4);
+        const double cost = (double)waves * ((r * Wp + 31) / 32 + 0.5);
+        if (cost < best) { best = cost; ry = r; }
+    }
     if (n4 > 65535 || (Hp + ry - 1) / ry > 65535) return fail(c, FXB_ERR_UNSUPPORTED, "Conv2D batch too large for the packed operand pass");
-    dim3 grid((Cp + XN_CT - 1) / XN_CT, (Hp + ry - 1) / ry, n4);
+    dim3 grid(gx, (Hp + ry - 1) / ry, n4);
     static bool carveout_set[64] = {};
     if (!carveout_set[c->device & 63]) {  // 34 KB of static shared memory per block: ask for room for four blocks per SM
         FXB_CUDA_OK(c, cudaFuncSetAttribute(pack_xn_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
