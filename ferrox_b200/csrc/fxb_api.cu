@@ -7,7 +7,7 @@ namespace fxb {
 thread_local std::string g_tls_error;
 }
 
-extern "C" int fxb_version(void) { return 110; }
+extern "C" int fxb_version(void) { return 120; }
 
 namespace fxb {
 // Self-test of the bounded-wait convention every kernel of the library follows: one warp waits on an

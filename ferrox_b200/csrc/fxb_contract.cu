@@ -1770,7 +1770,11 @@ static int linear_fwd_impl(Context* c, const T* X, const T* W, const T* bias, T*
         if (B == 0) return FXB_OK;
         FXB_CHECK_ARG(c, X && W && Y, "Matrix multiplication got a null buffer");
         FXB_CHECK_ARG(c, act >= FXB_ACT_NONE && act <= FXB_ACT_TANH, "Unknown activation code");
-        skinny_linear_fwd_kernel<T><<<(unsigned)B, 256, 0, st>>>(X, W, bias, Y, (int)B, (int)in, (int)out, act);
+        // four rows per block once that still gives two blocks per SM; one row per block for small batches
+        if (B >= (int64_t)8 * c->sm_count)
+            skinny_linear_fwd_kernel<T, 4><<<(unsigned)((B + 3) / 4), 256, 0, st>>>(X, W, bias, Y, (int)B, (int)in, (int)out, act);
+        else
+            skinny_linear_fwd_kernel<T, 1><<<(unsigned)B, 256, 0, st>>>(X, W, bias, Y, (int)B, (int)in, (int)out, act);
         return launch_status(c, "skinny_linear_fwd_kernel");
     }
     // (the workspace only serves the tensor-map path: this product never splits K)
@@ -1808,8 +1812,12 @@ static int linear_bwd_impl(Context* c, const T* X, const T* W, const T* Y, const
                 if (rc) return rc;
             }
             if (dX) {
-                dim3 gx((unsigned)B, (unsigned)((in + 255) / 256));
-                skinny_linear_dx_kernel<T><<<gx, 256, 0, st>>>(dY, aux, W, dX, (int)in, (int)out, act, c->sigmoid_grad_math);
+                // rows per block: as many as leave about four blocks per SM (at most SKINNY_DX_ROWS)
+                const int64_t slices = (in + 255) / 256;
+                int rows = (int)std::max<int64_t>(1, std::min<int64_t>(SKINNY_DX_ROWS, B * slices / ((int64_t)c->sm_count * 4)));
+                dim3 gx((unsigned)((B + rows - 1) / rows), (unsigned)slices);
+                skinny_linear_dx_kernel<T><<<gx, 256, 0, st>>>(dY, aux, W, dX, (int)B, (int)in, (int)out, act, c->sigmoid_grad_math,
+                                                               rows);
                 rc = launch_status(c, "skinny_linear_dx_kernel");
             }
             return rc;

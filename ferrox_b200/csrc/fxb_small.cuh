@@ -11,66 +11,87 @@ namespace fxb {
 
 constexpr int SKINNY_MAXO = 16;
 
-// Y[b][o] = act(sum_i X[b][i] * W[o][i] + bias[o]); one block of 256 threads per row b: every thread
-// takes the columns i = t, t + 256, ..., the partial sums are added by warp shuffles and then over
-// the eight warps in warp order.
-template <typename T>
+// Y[b][o] = act(sum_i X[b][i] * W[o][i] + bias[o]); one block of 256 threads per R rows: every thread takes the
+// columns i = t, t + 256, ..., loads the `out` weights of a column once and uses them for the R rows (the
+// weights are what the blocks re-read from L2: R = 4 quarters that traffic); the partial sums are added by
+// warp shuffles and then over the eight warps in warp order.  The result does not depend on R.
+template <typename T, int R>
 __global__ void __launch_bounds__(256) skinny_linear_fwd_kernel(const T* __restrict__ X, const T* __restrict__ W,
                                                                 const T* __restrict__ bias, T* __restrict__ Y, int B, int in,
                                                                 int out, int act) {
-    __shared__ T red[8][SKINNY_MAXO];
+    __shared__ T red[R][8][SKINNY_MAXO];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int b = blockIdx.x;
-    T acc[SKINNY_MAXO];
+    const int b0 = blockIdx.x * R;
+    T acc[R][SKINNY_MAXO];
 #pragma unroll
-    for (int o = 0; o < SKINNY_MAXO; ++o) acc[o] = T(0);
-    const T* xr = X + (int64_t)b * in;
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int o = 0; o < SKINNY_MAXO; ++o) acc[r][o] = T(0);
 #pragma unroll 2
     for (int i = threadIdx.x; i < in; i += 256) {
-        const T xv = __ldg(xr + i);
+        T xv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) xv[r] = b0 + r < B ? __ldg(X + (int64_t)(b0 + r) * in + i) : T(0);
 #pragma unroll
         for (int o = 0; o < SKINNY_MAXO; ++o)
-            if (o < out) acc[o] += xv * __ldg(W + (int64_t)o * in + i);
+            if (o < out) {
+                const T wv = __ldg(W + (int64_t)o * in + i);
+#pragma unroll
+                for (int r = 0; r < R; ++r) acc[r][o] += xv[r] * wv;
+            }
     }
 #pragma unroll
-    for (int o = 0; o < SKINNY_MAXO; ++o) {
-        T v = acc[o];
-        v += __shfl_xor_sync(0xffffffffu, v, 16);
-        v += __shfl_xor_sync(0xffffffffu, v, 8);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        if (lane == 0) red[warp][o] = v;
-    }
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int o = 0; o < SKINNY_MAXO; ++o) {
+            T v = acc[r][o];
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            if (lane == 0) red[r][warp][o] = v;
+        }
     __syncthreads();
-    if (threadIdx.x < out) {
-        const int o = threadIdx.x;
-        const T v = ((red[0][o] + red[1][o]) + (red[2][o] + red[3][o])) + ((red[4][o] + red[5][o]) + (red[6][o] + red[7][o]));
-        Y[(int64_t)b * out + o] = act_apply<T>(v + (bias ? __ldg(bias + o) : T(0)), act);
+    for (int e = threadIdx.x; e < R * out; e += 256) {
+        const int r = e / out, o = e - r * out;
+        if (b0 + r < B) {
+            const T v = ((red[r][0][o] + red[r][1][o]) + (red[r][2][o] + red[r][3][o])) +
+                        ((red[r][4][o] + red[r][5][o]) + (red[r][6][o] + red[r][7][o]));
+            Y[(int64_t)(b0 + r) * out + o] = act_apply<T>(v + (bias ? __ldg(bias + o) : T(0)), act);
+        }
     }
 }
 
-// dX[b][i] = sum_o dZ[b][o] * W[o][i], dZ = dY * act'(Y); grid (B, ceil(in/256)): the batch index is
-// the x dimension of the grid, which has no 65535 limit.
+// dX[b][i] = sum_o dZ[b][o] * W[o][i], dZ = dY * act'(Y); grid (ceil(B / rows), ceil(in/256)): a block keeps the
+// `out` weights of its 256 columns in registers and walks over `rows` (<= SKINNY_DX_ROWS) batch rows, so the
+// weights are read once per block instead of once per row.
+constexpr int SKINNY_DX_ROWS = 32;
 template <typename T>
 __global__ void __launch_bounds__(256) skinny_linear_dx_kernel(const T* __restrict__ dY, const T* __restrict__ Yact,
-                                                               const T* __restrict__ W, T* __restrict__ dX, int in, int out,
-                                                               int act, int sig_math) {
-    __shared__ T dz[SKINNY_MAXO];
-    const int b = blockIdx.x;
-    if (threadIdx.x < out) {
-        T v = __ldg(dY + (int64_t)b * out + threadIdx.x);
-        if (Yact) v *= act_grad_factor<T>(__ldg(Yact + (int64_t)b * out + threadIdx.x), act, sig_math);
-        dz[threadIdx.x] = v;
+                                                               const T* __restrict__ W, T* __restrict__ dX, int B, int in, int out,
+                                                               int act, int sig_math, int rows) {
+    __shared__ T dz[SKINNY_DX_ROWS * SKINNY_MAXO];
+    const int b0 = blockIdx.x * rows;
+    const int nr = min(rows, B - b0);
+    for (int e = threadIdx.x; e < nr * out; e += 256) {
+        T v = __ldg(dY + (int64_t)b0 * out + e);
+        if (Yact) v *= act_grad_factor<T>(__ldg(Yact + (int64_t)b0 * out + e), act, sig_math);
+        dz[e] = v;
     }
     __syncthreads();
     const int i = blockIdx.y * blockDim.x + threadIdx.x;
     if (i >= in) return;
-    T acc = T(0);
+    T w[SKINNY_MAXO];
 #pragma unroll
-    for (int o = 0; o < SKINNY_MAXO; ++o)
-        if (o < out) acc += dz[o] * __ldg(W + (int64_t)o * in + i);
-    dX[(int64_t)b * in + i] = acc;
+    for (int o = 0; o < SKINNY_MAXO; ++o) w[o] = o < out ? __ldg(W + (int64_t)o * in + i) : T(0);
+    for (int r = 0; r < nr; ++r) {
+        T acc = T(0);
+#pragma unroll
+        for (int o = 0; o < SKINNY_MAXO; ++o)
+            if (o < out) acc += dz[r * out + o] * w[o];
+        dX[(int64_t)(b0 + r) * in + i] = acc;
+    }
 }
 
 // Partial dW / db over one chunk of `rows_per_chunk` (<= SKINNY_ROWS) batch rows: part[chunk][o][i] = sum_b dZ[b][o] * X[b][i],
