@@ -57,7 +57,7 @@ def synthetic_batch(rng, n, dtype=np.float32):
 
 def workload_config(world, graph=False):
     """The `config` object of the JSON line (the same for both arms)."""
-    return {"launch": "CUDA graph replay" if graph else "eager launches","workload": "deep_cnn_train_step_global_batch_1024", "global_batch": GLOBAL_BATCH,
+    return {"workload": "deep_cnn_train_step_global_batch_1024", "global_batch": GLOBAL_BATCH,
             "per_gpu_batch": GLOBAL_BATCH // world, "optimizer": "adam", "math": "3xTF32 on tcgen05, f32 accumulate",
             "parallelism": f"dp{world}", "l2": "256 MiB buffer written, then a second 256 MiB read, between timed steps (not timed)",
             "allreduce": "NCCL sum, 2 buckets (last layers holding half of the parameters first), overlapped with backward"
@@ -613,7 +613,8 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "f32", "data": "synthetic", "config": workload_config(world, args.graph),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_pin.numel() * 4 + t_pin.numel() * 4) * world,
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "loss": loss_value,
+            "gpu_launches": int(launches), "launch_mode": "CUDA graph replay" if args.graph else "eager launches",
+            "clocks": clocks, "roofline": roofline, "loss": loss_value,
         }
         if world == 1:
             rate, sec = cpu_reference_step_rate(CPU_SAMPLE_IMAGES, 3, 1)
