@@ -937,6 +937,9 @@ static int conv_fprop_tma(Context* c, const float* X, const float* W, const floa
         prm.out = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up256(w.bytes));
     }
     set_vec_store(prm);
+    // several column tiles: walk them row-tile group by row-tile group, so that the second column tile finds the
+    // image tiles of the first one still in L2
+    if (prm.tn > 1 && fs.splits == 1) prm.group_m = 8;
     if (chain != nullptr && chain->emit.hi != nullptr && fs.splits == 1) {
         prm.emit = chain->emit;
         chain->emitted = true;
@@ -1168,6 +1171,7 @@ static int conv_dgrad_tma(Context* c, const float* dY, const float* Yact, const 
             q.tn = (g.C + bn - 1) / bn;
             q.ncols = g.C;
             q.ncls = 1;
+            if (q.tn > 1) q.group_m = 8;  // (as in the forward pass: column tiles of a row-tile group back to back)
             q.kchunks[0] = chunks;
             q.three_pass = c->math_mode == FXB_MATH_3XTF32 ? 1 : 0;
             q.drain_group = c->drain_group;

@@ -95,7 +95,8 @@ struct TmaConvParams {
     // forward convolutions (ncls == 1, splits == 1): also write the activated output as the next layer's class slabs
     SlabEmit emit;
     // > 0: items walk the tiles in groups of group_m row tiles (all column tiles of a group before the next
-    // group), so that CTAs running side by side share operand rows in L2.  splits == 1, ncls == 1 only.
+    // group), so that CTAs running side by side share operand rows in L2.  splits == 1 only (with merged stride
+    // classes the class stays the fastest index and the grouping applies to the (row tile, column tile) part).
     int group_m = 0;
 };
 
