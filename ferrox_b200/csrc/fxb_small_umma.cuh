@@ -19,7 +19,7 @@
 
 namespace fxb {
 
-constexpr int FLW_STAGES = 2;
+constexpr int FLW_STAGES = 2;                    // operand stages (four measured the same)
 constexpr int FLW_BK = 32;                       // pixels per stage
 constexpr int FLW_KCH = FLW_BK / 4;              // 16-byte chunks per row and stage
 constexpr int FLW_LBO_A = 128 * 16 + 16;         // chunk pitch (bytes); the extra 16 bytes spread the chunks of
@@ -28,9 +28,10 @@ constexpr int FLW_A_BYTES = FLW_KCH * FLW_LBO_A;
 constexpr int FLW_B_BYTES = FLW_KCH * FLW_LBO_B;
 constexpr int FLW_STAGE_BYTES = 2 * FLW_A_BYTES + 2 * FLW_B_BYTES;
 constexpr int FLW_AUX_BYTES = 1024;
-// Landing ring of the dY / Y loads: FLW_RING tiles, per tile and tensor one 16-byte cell per loading thread.
-// With ~3 us of loaded DRAM latency the chip needs ~20 MB of reads in flight to run at the HBM rate; registers
-// cannot hold that many, asynchronous copies into shared memory can (8 tiles x 16 KB per SM).
+// Landing ring of the dY / Y loads: FLW_RING tiles, per tile and tensor one 16-byte cell per loading thread
+// (asynchronous copies, 8 tiles x 16 KB in flight per SM, no registers held while they fly).  Measured: the ring
+// and a four-tile register prefetch run equally fast, because the kernel is bound by the hand-offs of its short
+// stages, not by memory (without any global load it takes 218 us instead of 247 us per call at batch 1024).
 constexpr int FLW_RING = 8;
 constexpr int FLW_RING_BYTES = FLW_RING * 2 * 512 * 16;
 constexpr int FLW_SMEM_BYTES = FLW_AUX_BYTES + FLW_STAGES * FLW_STAGE_BYTES + FLW_RING_BYTES;
@@ -39,7 +40,7 @@ constexpr int FLW_B_STAGERS = 256;               // warps 16-23: one im2col chun
 constexpr int FLW_STAGERS = FLW_A_STAGERS + FLW_B_STAGERS;
 constexpr int FLW_MMA_WARP = FLW_STAGERS / 32;
 constexpr int FLW_THREADS = FLW_STAGERS + 32 + 128;  // + the MMA warp + four drain warps
-constexpr int FLW_PREFETCH = 4;                  // tiles of global loads in flight per staging thread
+constexpr int FLW_PREFETCH = 4;                  // tiles of gathered loads in flight per im2col staging thread
 constexpr int FLW_GROUP = 4;                     // stages accumulated in TMEM between two drains
 constexpr int FLW_TMEM_COLS = 128;               // correction (32) + two main accumulators (32 each)
 
@@ -107,9 +108,8 @@ firstlayer_wgrad_umma_kernel(const float* __restrict__ x, const float* __restric
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    // Staging.  A warp keeps only a handful of load instructions in flight, so the bytes in flight per SM grow with
-    // the number of loading warps: sixteen warps load dY / Y (one 16-byte chunk of each per thread and stage), eight
-    // more gather the im2col chunks; every thread has FLW_PREFETCH stages of loads outstanding.
+    // Staging: sixteen warps bring in dY / Y (one 16-byte chunk of each per thread and stage), eight more gather the
+    // im2col chunks (twenty-four staging warps measured 15 % faster than eight doing the same work).
     const auto tile_of = [&](int i) { return first_tile + i; };
     const auto stage_ready = [&](int i, bool& ok) -> int {  // waits until stage i's buffer is free; returns its index
         const int s = i % FLW_STAGES;
