@@ -78,3 +78,27 @@ def test_two_rank_bucketed_allreduce_matches_global_batch():
         assert p.exitcode == 0
     for rank, err, lerr in res:
         assert err < 1e-12 and lerr < 1e-12, (rank, err, lerr)
+
+
+def test_bucket_plans_of_the_benchmark_networks():
+    """The tail bucket is the shortest run of last layers that holds at least half of the parameters; bucket lists
+    tile the flat gradient buffer (plus the loss slot) exactly once, last layers first."""
+    from ferrox_b200.train import deep_cnn_layers, flat_offsets, layer_param_shapes, mlp_layers, plan_bucket_list, plan_buckets
+    for make, want_split in ((deep_cnn_layers, 3), (mlp_layers, 1)):
+        layers, in_shape = make()
+        offs = flat_offsets(layer_param_shapes(layers, in_shape))
+        nparams = offs[-1][2]
+        split_layer, split_off = plan_buckets(offs, nparams)
+        assert split_layer == want_split and split_off == offs[split_layer][0]
+        if split_layer > 1 or 2 * (nparams - split_off) >= nparams:
+            assert 2 * (nparams - split_off) >= nparams                  # the tail holds at least half ...
+        else:
+            assert split_layer == 1                                      # ... or everything but the first layer
+        if split_layer + 1 < len(offs):
+            assert 2 * (nparams - offs[split_layer + 1][0]) < nparams    # and no shorter tail holds half
+        for splits in (None, [3, 1], [1], [4, 3, 2, 1], [0, 99]):
+            buckets = plan_bucket_list(offs, nparams, splits)
+            assert buckets[0][2] == nparams + 1 and buckets[-1][1] == 0
+            assert all(a[1] == b[2] for a, b in zip(buckets, buckets[1:]))
+            assert [b[0] for b in buckets] == sorted({b[0] for b in buckets}, reverse=True)
+    assert plan_buckets(offs, nparams, tail_layers=1)[0] == len(offs) - 1
