@@ -561,3 +561,12 @@ def test_optimizer_steps(ops, oracle, dtype):
         assert_parity(pt, pc, "adam")
         assert_parity(mt, m, "adam m")
         assert_parity(vt, v, "adam v")
+    # the two cases of the reference's own Adam tests (src/nn/optim/adam.rs:568-633): p = 1, g = 0.5, lr = 0.1 and
+    # AdamW with zero gradient (lr = 0.1, weight decay 0.01); the reference asserts that the parameter decreases
+    tol = 1e-6 if dtype == np.float32 else 1e-12
+    pt, mt, vt = dev(np.ones(1, dtype)), dev(np.zeros(1, dtype)), dev(np.zeros(1, dtype))
+    ops.adam_step_(pt, dev(np.full(1, 0.5, dtype)), mt, vt, 1, lr=0.1)
+    assert host(pt)[0] < 1.0 and abs(host(pt)[0] - (1.0 - 0.1 * 0.5 / (0.5 + 1e-8))) <= tol
+    pt, mt, vt = dev(np.ones(1, dtype)), dev(np.zeros(1, dtype)), dev(np.zeros(1, dtype))
+    ops.adam_step_(pt, dev(np.zeros(1, dtype)), mt, vt, 1, lr=0.1, weight_decay=0.01)
+    assert host(pt)[0] < 1.0 and abs(host(pt)[0] - (1.0 - 0.1 * 0.01)) <= tol

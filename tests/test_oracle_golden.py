@@ -215,3 +215,22 @@ def test_global_avg_pool_matches_independent_autograd(oracle):
     yt.backward(torch.tensor(dy))
     assert np.abs(oracle.global_avg_pool_fwd(x) - yt.detach().numpy()).max() < 1e-13
     assert np.abs(oracle.global_avg_pool_bwd(dy, x.shape) - xt.grad.numpy()).max() < 1e-13
+
+
+def test_adam_cases_of_the_reference_tests(oracle):
+    """The two Adam cases the reference tests (src/nn/optim/adam.rs:568-633).  The reference asserts only that the
+    parameter decreases; the closed forms of the first step pin the values as well: with bias correction the first
+    update is lr * g / (|g| + eps) whatever the betas, and the decoupled weight decay of Adam::adamw
+    (adam.rs:259-275) subtracts lr * wd * p before it."""
+    for dt, tol in ((np.float32, 1e-7), (np.float64, 1e-12)):
+        # test_adam_basic_step: p = 1, g = 0.5, Adam::with_defaults(0.1)
+        p, m, v = np.ones(1, dt), np.zeros(1, dt), np.zeros(1, dt)
+        oracle.adam_step(p, np.full(1, 0.5, dt), m, v, 1, lr=0.1)
+        assert p[0] < 1.0
+        assert abs(p[0] - (1.0 - 0.1 * 0.5 / (0.5 + 1e-8))) <= tol
+        assert abs(m[0] - 0.05) <= tol and abs(v[0] - 0.00025) <= tol
+        # test_adam_weight_decay: p = 1, g = 0, Adam::adamw(0.1, 0.01): only the decay acts
+        p, m, v = np.ones(1, dt), np.zeros(1, dt), np.zeros(1, dt)
+        oracle.adam_step(p, np.zeros(1, dt), m, v, 1, lr=0.1, wd=0.01)
+        assert p[0] < 1.0
+        assert abs(p[0] - (1.0 - 0.1 * 0.01)) <= tol
