@@ -4,7 +4,7 @@
 Run in a container where the reference checkout is present:
     python tests/golden/make_golden.py /path/to/ferrox
 The numbers are read from the reference's Rust unit tests as text (nothing is retyped):
-  src/ops/mod.rs            relu/sigmoid/tanh/matmul/transpose/sum/mean/softmax/conv2d tests
+  src/ops/mod.rs            relu/sigmoid/tanh/add/mul/matmul/transpose/sum/mean/softmax/conv2d tests
   src/backend/tensor.rs     test_matmul_operation, activations, sum/mean
   src/nn/optim/sgd.rs       test_sgd_basic_step
 The JSON is committed so the tests run where the reference checkout is absent.
@@ -146,6 +146,11 @@ def main(ref):
     b = body(ten, "test_broadcast_to")
     G["test_broadcast_to"] = {"source": "src/backend/tensor.rs::test_broadcast_to", "input": arrays(b)[0], "in_shape": [2],
                               "target_shape": [3, 2]}
+    # element-wise add / mul (gradient accumulation and the mask products of the backward rules)
+    for name, op in (("add_operation", "add"), ("mul_operation", "mul")):
+        a = arrays(body(ops, name))
+        G[name] = {"source": f"src/ops/mod.rs::{name}", "op": op, "a": a[0], "b": a[1], "shape": a[2], "expected": a[3],
+                   "tol": 1e-6}
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_known_answers.json")
     with open(out, "w") as f:
         json.dump(G, f, indent=1)

@@ -59,6 +59,9 @@ def test_golden_vectors_through_cuda(ops, golden):
     g = golden["matrix_transpose"]
     a = np.array(g["input"], np.float32).reshape(2, 3)
     assert host(ops.transpose(dev(a))).ravel().tolist() == g["expected"]
+    for name, fn in (("add_operation", ops.add), ("mul_operation", ops.mul)):
+        g = golden[name]
+        assert host(fn(dev(np.array(g["a"], np.float32)), dev(np.array(g["b"], np.float32)))).tolist() == g["expected"], name
     for name in ("conv2d_simple_forward", "conv2d_test", "conv2d_edge_cases"):
         g = golden[name]
         y = ops.conv2d_forward(dev(np.array(g["x"], np.float32).reshape(g["x_shape"])),

@@ -19,6 +19,14 @@ def test_golden_activations(golden, oracle):
     assert abs(y[0]) < 1e-6 and y[1] > 0.99 and y[2] < -0.99
 
 
+def test_golden_add_mul(golden):
+    """Element-wise add / mul have no oracle function of their own: the restatement of `&a + &b` / `&a * &b`
+    (src/backend/storage/cpu.rs) is the numpy operator, which the GPU tests compare with bit for bit."""
+    for name, fn in (("add_operation", np.add), ("mul_operation", np.multiply)):
+        g = golden[name]
+        assert fn(np.array(g["a"], np.float32), np.array(g["b"], np.float32)).tolist() == g["expected"], name
+
+
 def test_golden_matmul_transpose(golden, oracle):
     for name in ("matrix_multiply", "test_matmul_operation"):
         g = golden[name]
